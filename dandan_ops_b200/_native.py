@@ -1,0 +1,181 @@
+"""ctypes binding of the C-ABI library (include/b2_w4a16.h) and tensor-level wrappers.
+
+The library is the only compute path of the package: if it cannot be loaded, every
+operation that needs it raises ImportError - there is no eager or CPU stand-in.
+"""
+import ctypes
+import threading
+
+import torch
+
+from . import build as _build
+
+OK = 0
+ROUTE_AUTO, ROUTE_STREAM, ROUTE_TCGEN05 = 0, 1, 2
+ROUTE_NAMES = {ROUTE_STREAM: "b200_stream", ROUTE_TCGEN05: "b200_tcgen05"}
+STREAM_MAX_M = 64
+TICKET_BYTES = 16384
+
+_lib = None
+_lock = threading.Lock()
+
+_i64, _vp, _int = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+_SIGNATURES = {
+    "b2_w4a16_contract_version": (_int, []),
+    "b2_w4a16_last_error": (ctypes.c_char_p, []),
+    "b2_w4a16_launch_count": (_i64, []),
+    "b2_w4a16_native_bytes": (_i64, [_i64, _i64]),
+    "b2_w4a16_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "b2_w4a16_unrepack": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "b2_w4a16_pack": (_int, [_vp, _i64, _i64, _vp, _vp]),
+    "b2_w4a16_dequantize": (_int, [_vp, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_dequantize_fp16": (_int, [_vp, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "b2_w4a16_status": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_uint)]),
+    "b2_w4a16_linear": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_linear_route": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
+    "b2_w4a16_plan": (_int, [_i64, _i64, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int),
+                             ctypes.POINTER(_int), ctypes.POINTER(_int)]),
+}
+EXPORTS = tuple(_SIGNATURES)
+
+
+def library_path():
+    return _build.LIB_PATH
+
+
+def load():
+    """Load lib/libb2w4a16.so (built by `python -m dandan_ops_b200.build`)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not path.is_file():
+            raise ImportError(f"{path} is missing: run `python -m dandan_ops_b200.build` "
+                              "(the package has no other compute path)")
+        lib = ctypes.CDLL(str(path))
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(lib, name)   # AttributeError here = stale binary
+            fn.restype, fn.argtypes = restype, argtypes
+        if lib.b2_w4a16_contract_version() != 2:
+            raise ImportError("incompatible W4A16 contract version in " + str(path))
+        _lib = lib
+    return _lib
+
+
+def _check(rc):
+    if rc != OK:
+        raise RuntimeError("b2_w4a16: " + _lib.b2_w4a16_last_error().decode())
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def launch_count():
+    return int(load().b2_w4a16_launch_count())
+
+
+def native_bytes(n, k):
+    return int(load().b2_w4a16_native_bytes(n, k))
+
+
+def repack(packed, scales, zeros, k):
+    """Reference-layout CUDA tensors -> native image (uint8 tensor)."""
+    lib = load()
+    n = packed.shape[0]
+    size = lib.b2_w4a16_native_bytes(n, k)
+    if size <= 0:
+        raise RuntimeError("b2_w4a16: W4A16 dimensions exceed the kernel index range")
+    with torch.cuda.device(packed.device):
+        image = torch.empty(size, dtype=torch.uint8, device=packed.device)
+        _check(lib.b2_w4a16_repack(packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                   n, k, image.data_ptr(), _stream()))
+    return image
+
+
+def unrepack(image, n, k):
+    lib = load()
+    dev = image.device
+    words, groups = (k + 7) // 8, (k + 63) // 64
+    with torch.cuda.device(dev):
+        packed = torch.empty((n, words), dtype=torch.int32, device=dev)
+        scales = torch.empty((n, groups), dtype=torch.float32, device=dev)
+        zeros = torch.empty((n, groups), dtype=torch.int32, device=dev)
+        _check(lib.b2_w4a16_unrepack(image.data_ptr(), n, k, packed.data_ptr(), scales.data_ptr(),
+                                     zeros.data_ptr(), _stream()))
+    return packed, scales, zeros
+
+
+def pack(codes):
+    lib = load()
+    n, k = codes.shape
+    with torch.cuda.device(codes.device):
+        out = torch.empty((n, (k + 7) // 8), dtype=torch.int32, device=codes.device)
+        _check(lib.b2_w4a16_pack(codes.data_ptr(), n, k, out.data_ptr(), _stream()))
+    return out
+
+
+def dequantize(image, n, k, dtype=torch.float32):
+    lib = load()
+    with torch.cuda.device(image.device):
+        out = torch.empty((n, k), dtype=dtype, device=image.device)
+        fn = lib.b2_w4a16_dequantize if dtype == torch.float32 else lib.b2_w4a16_dequantize_fp16
+        _check(fn(image.data_ptr(), n, k, out.data_ptr(), k, _stream()))
+    return out
+
+
+def plan(m, n, k):
+    lib = load()
+    route, splits, grid, rows = _int(), _int(), _int(), _int()
+    _check(lib.b2_w4a16_plan(m, n, k, ctypes.byref(route), ctypes.byref(splits), ctypes.byref(grid),
+                             ctypes.byref(rows)))
+    return {"route": ROUTE_NAMES.get(route.value, str(route.value)), "k_splits": splits.value,
+            "grid": grid.value, "rows_per_launch": rows.value}
+
+
+# One scratch buffer per (device, stream): kernels on one stream run in order, so every
+# layer launched there can share it.  The ticket prefix is zero on allocation and every
+# kernel leaves it zero.
+_workspaces = {}
+
+
+def workspace(device, nbytes):
+    key = (device.index, _stream())
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def status(device=None):
+    """Sticky status word of the current stream's workspace (synchronizes; 0 = ok)."""
+    lib = load()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(device):
+        ws = _workspaces.get((device.index, _stream()))
+        if ws is None:
+            return 0
+        word = ctypes.c_uint(0)
+        _check(lib.b2_w4a16_status(ws.data_ptr(), _stream(), ctypes.byref(word)))
+    return int(word.value)
+
+
+def linear(x, image, n, k, route=ROUTE_AUTO, out=None):
+    """y[M,N] = x[M,K] @ W^T on the current stream.  x must be CUDA FP16 with unit inner stride."""
+    lib = load()
+    m = x.shape[0]
+    with torch.cuda.device(x.device):
+        y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
+        if m == 0:
+            return y
+        need = lib.b2_w4a16_workspace_bytes(m, n, k)
+        ws = workspace(x.device, need)
+        _check(lib.b2_w4a16_linear_route(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(), y.data_ptr(),
+                                         y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), _stream(), route))
+    return y

@@ -1,0 +1,300 @@
+// C ABI of the engine: argument checks, launch planning and kernel launches.
+// Declarations and the per-function reference citations are in include/b2_w4a16.h.
+#include <cuda_runtime.h>
+#include <atomic>
+#include <climits>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/b2_w4a16.h"
+#include "layout.cuh"
+#include "layout_kernels.cuh"
+#include "stream_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_error;
+std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const std::string& msg) {
+    g_error = msg;
+    return code;
+}
+
+int cuda_fail(const char* what, cudaError_t e) {
+    return fail(B2_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int after_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(what, e);
+    return B2_OK;
+}
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+};
+
+// Per-device properties, read once per device.
+int device_info(DeviceInfo& out) {
+    static DeviceInfo cache[64];
+    static std::atomic<bool> ready[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail("cudaGetDevice", e);
+    if (dev < 0 || dev >= 64) return fail(B2_ERR_UNSUPPORTED, "device ordinal out of range");
+    if (!ready[dev].load(std::memory_order_acquire)) {
+        DeviceInfo info;
+        e = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail("cudaDeviceGetAttribute", e);
+        e = cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return cuda_fail("cudaDeviceGetAttribute", e);
+        cache[dev] = info;
+        ready[dev].store(true, std::memory_order_release);
+    }
+    out = cache[dev];
+    return B2_OK;
+}
+
+int check_dims(int64_t n, int64_t k) {
+    if (n <= 0 || k <= 0) return fail(B2_ERR_ARGUMENT, "n and k must be positive");
+    if (k > INT_MAX - 256 || n > INT_MAX - 64 || n * k > INT_MAX)
+        return fail(B2_ERR_RANGE, "W4A16 dimensions exceed the kernel index range");
+    return B2_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Launch plan of the streaming kernel.
+// ---------------------------------------------------------------------------------------
+struct StreamPlan {
+    int mt;            // 8-row tiles of x per launch: 1, 2, 4 or 8
+    int rows;          // rows of x per launch = min(m, 64)
+    int splits;        // K-splits
+    int kb_per_item;   // column blocks per split
+    int grid;          // CTAs of 8 warps (grid_x row-tile groups x splits)
+    int grid_x;
+    int64_t partial_bytes;
+};
+
+StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
+    StreamPlan p;
+    p.rows = int(m < B2_STREAM_MAX_M ? m : B2_STREAM_MAX_M);
+    p.mt = p.rows <= 8 ? 1 : p.rows <= 16 ? 2 : p.rows <= 32 ? 4 : 8;
+    // Aim at 16 resident warps per SM (8 when the accumulators are large); never split
+    // finer than one column block per item.
+    int64_t want = int64_t(sm_count > 0 ? sm_count : 148) * (p.mt <= 2 ? 16 : 8);
+    // one ticket per row tile; the last word of the ticket area is the status word
+    if (want > B2_W4A16_TICKET_BYTES / 4 - 1) want = B2_W4A16_TICKET_BYTES / 4 - 1;
+    int splits = 1;
+    if (d.n16 < want) splits = int((want + d.n16 - 1) / d.n16);
+    if (splits > d.kb) splits = d.kb;
+    p.kb_per_item = (d.kb + splits - 1) / splits;
+    p.splits = (d.kb + p.kb_per_item - 1) / p.kb_per_item;
+    const int64_t items = int64_t(p.splits) * d.n16;
+    p.grid_x = (d.n16 + b2::kWarps - 1) / b2::kWarps;
+    p.grid = p.grid_x * p.splits;
+    p.partial_bytes = p.splits > 1 ? items * p.mt * 512 : 0;
+    return p;
+}
+
+template <int MT, bool XVEC>
+int launch_stream_one(const b2::StreamArgs& a, dim3 grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_stream_kernel<MT, XVEC>;
+    // Opt in to >48 KB of dynamic shared memory once per device and instantiation.
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   b2::kStreamSmem);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<grid, 256, b2::kStreamSmem, s>>>(a);
+    return after_launch("w4a16_stream_kernel");
+}
+
+template <int MT>
+int launch_stream(const b2::StreamArgs& a, bool xvec, dim3 grid, cudaStream_t s) {
+    return xvec ? launch_stream_one<MT, true>(a, grid, s) : launch_stream_one<MT, false>(a, grid, s);
+}
+
+int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
+               const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s,
+               const DeviceInfo& dev) {
+    const int64_t ticket_bytes = B2_W4A16_TICKET_BYTES;
+    const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
+    for (int64_t m0 = 0; m0 < m; m0 += B2_STREAM_MAX_M) {
+        const int64_t rows = (m - m0) < B2_STREAM_MAX_M ? (m - m0) : B2_STREAM_MAX_M;
+        const StreamPlan p = plan_stream(rows, d, dev.sm_count);
+        if (workspace == nullptr || workspace_bytes < ticket_bytes + p.partial_bytes)
+            return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
+        b2::StreamArgs a;
+        a.x = static_cast<const __half*>(x) + m0 * ldx;
+        a.native = static_cast<const uint8_t*>(native);
+        a.y = static_cast<__half*>(y) + m0 * ldy;
+        a.ticket = static_cast<unsigned*>(workspace);
+        a.status = a.ticket + (B2_W4A16_TICKET_BYTES / 4 - 1);
+        a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ticket_bytes);
+        a.ldx = ldx; a.ldy = ldy;
+        a.m = int(rows); a.n = d.n; a.k = d.k;
+        a.n16 = d.n16; a.kb = d.kb;
+        a.kb_per_item = p.kb_per_item; a.splits = p.splits;
+        const dim3 grid(p.grid_x, p.splits);
+        int rc;
+        switch (p.mt) {
+            case 1: rc = launch_stream<1>(a, xvec, grid, s); break;
+            case 2: rc = launch_stream<2>(a, xvec, grid, s); break;
+            case 4: rc = launch_stream<4>(a, xvec, grid, s); break;
+            default: rc = launch_stream<8>(a, xvec, grid, s); break;
+        }
+        if (rc != B2_OK) return rc;
+    }
+    return B2_OK;
+}
+
+int64_t stream_workspace_bytes(int64_t m, const b2::Dims& d, int sm_count) {
+    int64_t need = 0;
+    // The first launch has the most rows; later chunks never need more.
+    const StreamPlan p = plan_stream(m, d, sm_count);
+    need = p.partial_bytes;
+    return B2_W4A16_TICKET_BYTES + need;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2_w4a16_contract_version(void) { return 2; }
+
+const char* b2_w4a16_last_error(void) { return g_error.c_str(); }
+
+int64_t b2_w4a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int64_t b2_w4a16_native_bytes(int64_t n, int64_t k) {
+    if (check_dims(n, k) != B2_OK) return 0;
+    return b2::native_bytes(b2::make_dims(n, k));
+}
+
+int b2_w4a16_repack(const int32_t* packed, const float* scales, const int32_t* zeros, int64_t n,
+                    int64_t k, void* native, void* stream) {
+    if (!packed || !scales || !zeros || !native) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (int rc = check_dims(n, k)) return rc;
+    if (reinterpret_cast<uintptr_t>(native) % 256) return fail(B2_ERR_ARGUMENT, "native image must be 256-byte aligned");
+    const b2::Dims d = b2::make_dims(n, k);
+    const int64_t blocks = int64_t(d.n16) * d.kb;
+    b2::repack_kernel<<<unsigned(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        packed, scales, zeros, d, static_cast<uint8_t*>(native));
+    return after_launch("repack_kernel");
+}
+
+int b2_w4a16_unrepack(const void* native, int64_t n, int64_t k, int32_t* packed, float* scales,
+                      int32_t* zeros, void* stream) {
+    if (!packed || !scales || !zeros || !native) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (int rc = check_dims(n, k)) return rc;
+    const b2::Dims d = b2::make_dims(n, k);
+    const int64_t total = int64_t(d.n) * d.words;
+    b2::unrepack_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(native), d, packed, scales, zeros);
+    return after_launch("unrepack_kernel");
+}
+
+int b2_w4a16_pack(const uint8_t* codes, int64_t n, int64_t k, int32_t* packed, void* stream) {
+    if (!codes || !packed) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (int rc = check_dims(n, k)) return rc;
+    const b2::Dims d = b2::make_dims(n, k);
+    const int64_t total = int64_t(d.n) * d.words;
+    b2::pack_kernel<<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, d, packed);
+    return after_launch("pack_kernel");
+}
+
+int b2_w4a16_dequantize(const void* native, int64_t n, int64_t k, float* out, int64_t ldo, void* stream) {
+    if (!native || !out) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (int rc = check_dims(n, k)) return rc;
+    if (ldo < k) return fail(B2_ERR_ARGUMENT, "ldo must be at least k");
+    const b2::Dims d = b2::make_dims(n, k);
+    const int64_t total = int64_t(d.n) * d.words;
+    b2::dequantize_kernel<float><<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(native), d, out, ldo);
+    return after_launch("dequantize_kernel");
+}
+
+int b2_w4a16_dequantize_fp16(const void* native, int64_t n, int64_t k, void* out, int64_t ldo, void* stream) {
+    if (!native || !out) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (int rc = check_dims(n, k)) return rc;
+    if (ldo < k) return fail(B2_ERR_ARGUMENT, "ldo must be at least k");
+    const b2::Dims d = b2::make_dims(n, k);
+    const int64_t total = int64_t(d.n) * d.words;
+    b2::dequantize_kernel<__half><<<unsigned((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(native), d, static_cast<__half*>(out), ldo);
+    return after_launch("dequantize_kernel");
+}
+
+int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, int* grid, int* rows_per_launch) {
+    if (int rc = check_dims(n, k)) return rc;
+    if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
+    DeviceInfo dev;
+    if (device_info(dev) != B2_OK) dev.sm_count = 148;   // planning also works without a device
+    const b2::Dims d = b2::make_dims(n, k);
+    const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
+    if (route) *route = B2_ROUTE_STREAM;
+    if (k_splits) *k_splits = p.splits;
+    if (grid) *grid = p.grid;
+    if (rows_per_launch) *rows_per_launch = p.rows;
+    return B2_OK;
+}
+
+int b2_w4a16_status(const void* workspace, void* stream, unsigned* status_host) {
+    if (!workspace || !status_host) return fail(B2_ERR_ARGUMENT, "null pointer");
+    const unsigned* word = static_cast<const unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1);
+    cudaError_t e = cudaMemcpyAsync(status_host, word, sizeof(unsigned), cudaMemcpyDeviceToHost,
+                                    static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail("b2_w4a16_status", e);
+    return B2_OK;
+}
+
+int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (check_dims(n, k) != B2_OK || m < 0) return B2_W4A16_TICKET_BYTES;
+    DeviceInfo dev;
+    if (device_info(dev) != B2_OK) dev.sm_count = 148;
+    return stream_workspace_bytes(m > 0 ? m : 1, b2::make_dims(n, k), dev.sm_count);
+}
+
+int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
+                          int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes,
+                          void* stream, int route) {
+    if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
+    if (int rc = check_dims(n, k)) return rc;
+    if (m == 0) return B2_OK;
+    if (!x || !native || !y) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (ldx < k || ldy < n) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+    if (m > INT_MAX - 128 || m * k > INT_MAX || m * n > INT_MAX)
+        return fail(B2_ERR_RANGE, "W4A16 dimensions exceed the kernel index range");
+    if (reinterpret_cast<uintptr_t>(native) % 16) return fail(B2_ERR_ARGUMENT, "native image must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(x) % 2 || reinterpret_cast<uintptr_t>(y) % 2)
+        return fail(B2_ERR_ARGUMENT, "x and y must be 2-byte aligned");
+    if (workspace && reinterpret_cast<uintptr_t>(workspace) % 16)
+        return fail(B2_ERR_ARGUMENT, "workspace must be 16-byte aligned");
+    DeviceInfo dev;
+    if (int rc = device_info(dev)) return rc;
+    if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
+    const b2::Dims d = b2::make_dims(n, k);
+    if (route == B2_ROUTE_AUTO) route = B2_ROUTE_STREAM;
+    if (route == B2_ROUTE_STREAM)
+        return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream), dev);
+    return fail(B2_ERR_UNSUPPORTED, "unknown or unavailable route");
+}
+
+int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
+                    int64_t n, int64_t k, void* workspace, int64_t workspace_bytes, void* stream) {
+    return b2_w4a16_linear_route(x, ldx, native, y, ldy, m, n, k, workspace, workspace_bytes, stream,
+                                 B2_ROUTE_AUTO);
+}
+
+}  // extern "C"

@@ -1,0 +1,134 @@
+/*
+ * b2_w4a16.h - C ABI of the B200 (sm_100a) W4A16 quantized-linear engine.
+ *
+ * Plain pointers and sizes only: no torch types, no C++ types, no exceptions.  Every
+ * function returns an int status (B2_OK == 0); b2_w4a16_last_error() gives the text of
+ * the calling thread's last failure.  All pointers except `*_host` arguments are device
+ * pointers on the CURRENT device; `stream` is a cudaStream_t passed as void* (NULL = the
+ * legacy default stream).  Calls are asynchronous, never synchronize, never read tensor
+ * values on the host and allocate nothing, so they may be captured into a CUDA graph.
+ *
+ * Each entry point names the reference interface it stands in for (paths inside the
+ * reference project, dandan-ops).
+ *
+ * Tensor conventions (row-major, contiguous unless a leading dimension is given):
+ *   packed  int32  [N, ceil(K/8)]   eight unsigned 4-bit codes per word, code j in bits 4j..4j+3
+ *   scales  float  [N, ceil(K/64)]  one step per output row and group of 64 inputs
+ *   zeros   int32  [N, ceil(K/64)]  zero points in 0..15
+ *   x       fp16   [M, K]  (row stride ldx elements)
+ *   y       fp16   [M, N]  (row stride ldy elements)
+ *   weight  w[n,k] = fp16_rn( fp32(code - zero) * step ),  y = fp16_rn( sum_k fp32(x)*fp32(w) )
+ * Only group size 64 exists in this ABI.
+ */
+#ifndef B2_W4A16_H
+#define B2_W4A16_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_OK 0
+#define B2_ERR_ARGUMENT 1    /* null pointer, non-positive size, misaligned native buffer */
+#define B2_ERR_CUDA 2        /* a CUDA runtime call or a kernel launch failed */
+#define B2_ERR_WORKSPACE 3   /* workspace smaller than b2_w4a16_workspace_bytes() */
+#define B2_ERR_RANGE 4       /* dimensions exceed the kernel index range */
+#define B2_ERR_UNSUPPORTED 5 /* device is not sm_100 or the requested route does not apply */
+
+/* Kernel families selectable through b2_w4a16_linear_route(). */
+#define B2_ROUTE_AUTO 0      /* regime by M: stream kernel up to B2_STREAM_MAX_M rows, tensor-memory GEMM above */
+#define B2_ROUTE_STREAM 1    /* weight-streaming kernel (any M, re-reads the weights every 64 rows) */
+#define B2_ROUTE_TCGEN05 2   /* TMA + tcgen05 GEMM with in-kernel INT4->FP16 converter */
+
+/* Largest M the weight-streaming kernel takes in one launch; B2_ROUTE_AUTO hands larger
+ * batches to the tensor-memory GEMM. */
+#define B2_STREAM_MAX_M 64
+
+/* Every workspace starts with this many bytes of arrival counters (one per 16-row tile;
+ * K is only split when a layer has fewer row tiles than this). */
+#define B2_W4A16_TICKET_BYTES 16384
+
+/* Contract version of the packed format and numerics; 2, as the reference's
+ * `w4a16_contract_version` op (dandan_ops/csrc/operators.cu:260). */
+int b2_w4a16_contract_version(void);
+
+/* Text of the calling thread's last error ("" if none). */
+const char* b2_w4a16_last_error(void);
+
+/* Bytes of the device-native weight image for an [N, K] layer (0 on bad sizes).
+ * The image holds the 4-bit codes, FP32 steps and 4-bit zero points tiled in
+ * 16-row x 256-column blocks of 2336 bytes: 0.5703 bytes per weight when N and K are
+ * multiples of 16 and 256.  The reference keeps 0.625 bytes per weight
+ * (QuantizedLinear.storage_bytes, dandan_ops/quantized_linear.py:176-178). */
+int64_t b2_w4a16_native_bytes(int64_t n, int64_t k);
+
+/* Reference layout -> native image.  `native` must be 256-byte aligned and
+ * b2_w4a16_native_bytes(n,k) long.  Replaces the layout half of pack_int4
+ * (dandan_ops/quantization.py:85-103): the reference kernels read that layout
+ * directly, this engine reads the tiled image. */
+int b2_w4a16_repack(const int32_t* packed, const float* scales, const int32_t* zeros,
+                    int64_t n, int64_t k, void* native, void* stream);
+
+/* Native image -> reference layout (exact inverse of b2_w4a16_repack; codes beyond K
+ * in the last word come back as 0, as pack_int4 writes them). */
+int b2_w4a16_unrepack(const void* native, int64_t n, int64_t k, int32_t* packed,
+                      float* scales, int32_t* zeros, void* stream);
+
+/* uint8 codes [N,K] (values 0..15) -> packed int32 [N, ceil(K/8)].
+ * Replaces pack_int4 (dandan_ops/quantization.py:85-103). */
+int b2_w4a16_pack(const uint8_t* codes, int64_t n, int64_t k, int32_t* packed, void* stream);
+
+/* Native image -> FP32 weights [N,K] (row stride ldo), bit-identical to
+ * dequantize_int4 (dandan_ops/quantization.py:124-143). */
+int b2_w4a16_dequantize(const void* native, int64_t n, int64_t k, float* out, int64_t ldo,
+                        void* stream);
+
+/* Same, rounded once more to FP16: the weights the linear kernels multiply by
+ * (`dequantize_int4(...).half()`, dandan_ops/quantized_linear.py:75-76). */
+int b2_w4a16_dequantize_fp16(const void* native, int64_t n, int64_t k, void* out_fp16,
+                             int64_t ldo, void* stream);
+
+/* Scratch bytes b2_w4a16_linear needs for this problem on the current device (always > 0).
+ * The first B2_W4A16_TICKET_BYTES bytes hold per-tile arrival counters: they must be
+ * ZERO before the first call that uses the buffer and every call leaves them zero (the
+ * last word of that area is a sticky status word, see b2_w4a16_status), so one buffer can
+ * serve any number of calls (and graph replays) on one stream.  Calls that may overlap on
+ * the GPU need separate workspaces.  b2_w4a16_linear always needs a workspace. */
+int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
+
+/* Reads the workspace's sticky status word into *status_host (0 = every kernel that used
+ * the workspace ran to completion; bit 0 = a warp gave up waiting for a weight copy and
+ * the outputs of that call are undefined).  SYNCHRONIZES the stream; diagnostics only. */
+int b2_w4a16_status(const void* workspace, void* stream, unsigned* status_host);
+
+/* y = x @ W^T for one layer.  Replaces the four reference ops
+ *   w4a16_gemv        dandan_ops/csrc/operators.cu:122-137
+ *   w4a16_gemm        dandan_ops/csrc/operators.cu:90-120
+ *   w4a16_small       dandan_ops/csrc/hgemm.cu:70-86
+ *   w4a16_tensorcore  dandan_ops/csrc/hgemm.cu:63-68
+ * with one engine that picks the kernel by M.  m == 0 returns B2_OK without a launch.
+ * Limits (as check_w4a16, dandan_ops/csrc/gemm_checks.h:22-25): m*k, m*n and n*k must
+ * each fit in int32. */
+int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
+                    int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes,
+                    void* stream);
+
+/* Same with an explicit kernel family (B2_ROUTE_*), for tests and benchmarks. */
+int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
+                          int64_t m, int64_t n, int64_t k, void* workspace,
+                          int64_t workspace_bytes, void* stream, int route);
+
+/* Which kernel family B2_ROUTE_AUTO picks for this problem (a B2_ROUTE_* value) and,
+ * through the optional out-parameters, the launch plan: K-splits, grid size, rows of x
+ * handled per launch.  Pure host arithmetic; used by execution_info(). */
+int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, int* grid,
+                  int* rows_per_launch);
+
+/* Number of kernels this library has launched from the calling process so far. */
+int64_t b2_w4a16_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2_W4A16_H */
