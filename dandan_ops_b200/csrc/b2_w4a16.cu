@@ -67,60 +67,69 @@ int check_dims(int64_t n, int64_t k) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Launch plan of the streaming kernel.
+// Launch plan of the streaming kernel (stream-K over persistent CTAs).
 // ---------------------------------------------------------------------------------------
 struct StreamPlan {
     int mt;            // 8-row tiles of x per launch: 1, 2, 4 or 8
     int rows;          // rows of x per launch = min(m, 64)
-    int splits;        // K-splits
-    int kb_per_item;   // column blocks per split
-    int grid;          // CTAs of 8 warps (grid_x row-tile groups x splits)
-    int grid_x;
+    int warps;         // warps (row tiles) per CTA: 16 or 4
+    int groups;        // row groups = ceil(n16 / warps)
+    long long steps;   // groups * column blocks
+    int grid;          // persistent CTAs
+    int max_parts;     // most CTAs that share one row group
     int64_t partial_bytes;
 };
 
 StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     StreamPlan p;
+    const int sms = sm_count > 0 ? sm_count : 148;
     p.rows = int(m < B2_STREAM_MAX_M ? m : B2_STREAM_MAX_M);
     p.mt = p.rows <= 8 ? 1 : p.rows <= 16 ? 2 : p.rows <= 32 ? 4 : 8;
-    // Aim at 16 resident warps per SM (8 when the accumulators are large); never split
-    // finer than one column block per item.
-    int64_t want = int64_t(sm_count > 0 ? sm_count : 148) * (p.mt <= 2 ? 16 : 8);
-    // one ticket per row tile; the last word of the ticket area is the status word
-    if (want > B2_W4A16_TICKET_BYTES / 4 - 1) want = B2_W4A16_TICKET_BYTES / 4 - 1;
-    int splits = 1;
-    if (d.n16 < want) splits = int((want + d.n16 - 1) / d.n16);
-    if (splits > d.kb) splits = d.kb;
-    p.kb_per_item = (d.kb + splits - 1) / splits;
-    p.splits = (d.kb + p.kb_per_item - 1) / p.kb_per_item;
-    const int64_t items = int64_t(p.splits) * d.n16;
-    p.grid_x = (d.n16 + b2::kWarps - 1) / b2::kWarps;
-    p.grid = p.grid_x * p.splits;
-    p.partial_bytes = p.splits > 1 ? items * p.mt * 512 : 0;
+    // 16-warp CTAs (one per SM) when the layer has at least two steps per SM for them,
+    // else 4-warp CTAs (four per SM) so that small layers still spread over the chip.
+    const long long steps16 = (long long)((d.n16 + 15) / 16) * d.kb;
+    p.warps = (steps16 >= 2LL * sms && p.mt <= 4) ? 16 : 4;
+    if (p.mt == 8) p.warps = 16;                      // the 16 KB x buffer of a 4-warp CTA cannot hold 64 rows
+    p.groups = (d.n16 + p.warps - 1) / p.warps;
+    p.steps = (long long)p.groups * d.kb;
+    const long long slots = (long long)sms * (p.warps == 16 ? 1 : 4);
+    p.grid = int(p.steps < slots ? p.steps : slots);
+    const long long per_cta = p.steps / p.grid;       // >= 1
+    long long parts = (d.kb + per_cta - 1) / per_cta + 1;
+    if (parts > p.grid) parts = p.grid;
+    p.max_parts = int(parts);
+    const long long split_tiles = (long long)(p.groups < p.grid ? p.groups : p.grid) * p.warps;
+    p.partial_bytes = p.grid > 1 ? split_tiles * p.max_parts * p.mt * 512 : 0;
     return p;
 }
 
-template <int MT, bool XVEC>
-int launch_stream_one(const b2::StreamArgs& a, dim3 grid, cudaStream_t s) {
-    auto kernel = b2::w4a16_stream_kernel<MT, XVEC>;
+template <int MT, bool XVEC, int W>
+int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_stream_kernel<MT, XVEC, W>;
+    constexpr int smem = b2::stream_smem_bytes(W);
     // Opt in to >48 KB of dynamic shared memory once per device and instantiation.
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   b2::kStreamSmem);
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
-    kernel<<<grid, 256, b2::kStreamSmem, s>>>(a);
+    kernel<<<grid, W * 32, smem, s>>>(a);
     return after_launch("w4a16_stream_kernel");
 }
 
 template <int MT>
-int launch_stream(const b2::StreamArgs& a, bool xvec, dim3 grid, cudaStream_t s) {
-    return xvec ? launch_stream_one<MT, true>(a, grid, s) : launch_stream_one<MT, false>(a, grid, s);
+int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaStream_t s) {
+    if constexpr (MT == 8) {
+        return xvec ? launch_stream_one<MT, true, 16>(a, grid, s) : launch_stream_one<MT, false, 16>(a, grid, s);
+    } else {
+        if (warps == 16)
+            return xvec ? launch_stream_one<MT, true, 16>(a, grid, s) : launch_stream_one<MT, false, 16>(a, grid, s);
+        return xvec ? launch_stream_one<MT, true, 4>(a, grid, s) : launch_stream_one<MT, false, 4>(a, grid, s);
+    }
 }
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
@@ -143,14 +152,13 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.ldx = ldx; a.ldy = ldy;
         a.m = int(rows); a.n = d.n; a.k = d.k;
         a.n16 = d.n16; a.kb = d.kb;
-        a.kb_per_item = p.kb_per_item; a.splits = p.splits;
-        const dim3 grid(p.grid_x, p.splits);
+        a.groups = p.groups; a.max_parts = p.max_parts; a.steps = p.steps;
         int rc;
         switch (p.mt) {
-            case 1: rc = launch_stream<1>(a, xvec, grid, s); break;
-            case 2: rc = launch_stream<2>(a, xvec, grid, s); break;
-            case 4: rc = launch_stream<4>(a, xvec, grid, s); break;
-            default: rc = launch_stream<8>(a, xvec, grid, s); break;
+            case 1: rc = launch_stream<1>(a, xvec, p.warps, p.grid, s); break;
+            case 2: rc = launch_stream<2>(a, xvec, p.warps, p.grid, s); break;
+            case 4: rc = launch_stream<4>(a, xvec, p.warps, p.grid, s); break;
+            default: rc = launch_stream<8>(a, xvec, p.warps, p.grid, s); break;
         }
         if (rc != B2_OK) return rc;
     }
@@ -158,11 +166,9 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
 }
 
 int64_t stream_workspace_bytes(int64_t m, const b2::Dims& d, int sm_count) {
-    int64_t need = 0;
     // The first launch has the most rows; later chunks never need more.
     const StreamPlan p = plan_stream(m, d, sm_count);
-    need = p.partial_bytes;
-    return B2_W4A16_TICKET_BYTES + need;
+    return B2_W4A16_TICKET_BYTES + p.partial_bytes;
 }
 
 }  // namespace
@@ -242,7 +248,7 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
     const b2::Dims d = b2::make_dims(n, k);
     const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
     if (route) *route = B2_ROUTE_STREAM;
-    if (k_splits) *k_splits = p.splits;
+    if (k_splits) *k_splits = p.max_parts;
     if (grid) *grid = p.grid;
     if (rows_per_launch) *rows_per_launch = p.rows;
     return B2_OK;

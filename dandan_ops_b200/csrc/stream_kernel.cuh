@@ -1,35 +1,38 @@
 // Weight-streaming kernel for the decode regime (M <= 64 rows of x per launch).
 //
-// The kernel is bound by HBM: every weight byte is read exactly once, 0.5703 B/weight.
-// A CTA of eight warps owns eight neighbouring row tiles (128 outputs) and one K-split;
-// each warp walks the native blocks of its own tile along K.
+// The kernel is bound by HBM and by instruction issue at the same time: every weight
+// byte is read exactly once (0.5703 B/weight) and every weight costs about three
+// instructions to decode exactly, so both the copy pipeline and the inner loop are kept
+// as lean as the arithmetic contract allows.
 //
-// Weights: every warp keeps a ring of kStages blocks in shared memory, filled by bulk
-// asynchronous copies (cp.async.bulk, one 2336-byte copy per block, completion counted
-// on an mbarrier).  The copies need no registers, so 16 warps per SM hold ~150 KB in
-// flight - several times what HBM latency x bandwidth asks for.  A lane reads its 73
-// bytes of a landed block with conflict-free 16-byte shared loads and immediately hands
-// the slot back to the copy engine.
+// Work split ("stream-K").  The layer is cut into steps = (group of 16 row tiles = 256
+// outputs) x (column block of 256 inputs).  Steps are numbered row-group-major and dealt
+// out in equal contiguous ranges to one persistent CTA per SM, so all SMs finish
+// together whatever the shape.  A CTA has 16 warps; warp w owns row tile 16*group + w
+// and keeps FP32 accumulators for it while the CTA walks along K.  Where a range ends
+// inside a row group, the partial tiles go to the workspace in fragment order and the
+// last CTA to arrive at that row tile (ticket counter, nobody waits) adds the partials
+// in contributor order - so the result does not depend on which CTA came last - writes
+// y and re-zeroes the ticket.
 //
-// Activations: x for a phase of up to 2048 columns is staged in shared memory once per
+// Weights: every warp keeps a ring of kStages native blocks in shared memory, filled by
+// bulk asynchronous copies (cp.async.bulk, one 2336-byte copy per block, completion
+// counted on an mbarrier).  The copies need no registers, so the 16 warps of an SM hold
+// ~150 KB in flight.  A lane reads its 73 bytes of a landed block with conflict-free
+// 16-byte shared loads and immediately hands the slot back to the copy engine.
+//
+// Activations: x for a phase of up to 4096 columns is staged in shared memory once per
 // CTA, laid out [64-column chunk][row][eight 16-byte pieces, XOR-swizzled] so that the
 // 16-byte read a lane makes for its MMA B fragments is conflict-free.
 //
 // Dequantization keeps the reference's arithmetic exactly:
 //     w = fp16_rn( fp32(code - zero) * step_fp32 )
-// but does the integer->FP32 conversion on the tensor cores.  `(word >> 8e) & 0x000F000F
-// | 0x64006400` turns a pair of 4-bit codes into the FP16 pair (1024+code); the codes of
-// the odd nibbles come out as (1024+16*code).  An m16n8k8 MMA of those raw fragments
-// with a constant selection matrix (identity, or identity/16) and the accumulator
-// preset to -(1024+zero) or -(64+zero) returns fp32(code - zero) for exactly the
-// elements the lane holds - every product and sum is an integer below 2^11, so nothing
-// is rounded.  One FP32 multiply by the step and one cvt.rn.f16x2.f32 finish the weight,
-// already laid out as the A fragment of the product MMA.  x^T is the B operand
-// (8 rows of x per MMA), accumulators are FP32.
-//
-// Split-K: partial tiles go to the workspace in fragment order; the last warp to arrive
-// at a row tile (ticket counter, no waiting) adds the partials in split order - the
-// result does not depend on which warp came last - writes y and re-zeroes the ticket.
+// `(word >> 8e) & 0x000F000F | 0x64006400` turns a pair of 4-bit codes into the FP16 pair
+// (1024+code); the odd nibbles come out as (1024+16*code).  One mixed-precision
+// instruction per weight (add.f32.f16 / fma.f32.f16, sm_100) turns that into the exact
+// FP32 integer code-zero, one FP32 multiply applies the step, and cvt.rn.f16x2.f32 rounds
+// a pair to FP16 - already laid out as the A fragment of an m16n8k16 MMA whose B
+// fragment is x^T (8 rows of x per MMA) and whose accumulators are FP32.
 //
 // Every wait in the kernel is bounded: a warp that gives up on an mbarrier records
 // kStatusCopyTimeout in the status word, stops computing and leaves through the normal
@@ -40,11 +43,14 @@
 namespace b2 {
 
 constexpr int kStages = 4;                   // ring depth per warp
-constexpr int kWarps = 8;                    // warps (row tiles) per CTA
-constexpr int kBarBytes = 256;               // 8 warps x 4 stages x 8 B
-constexpr int kRingBytes = kWarps * kStages * kBlockBytes;   // 74752
-constexpr int kXBytes = 32768;               // staged activations per phase
-constexpr int kStreamSmem = kBarBytes + kRingBytes + kXBytes;
+// Shared-memory budget of a CTA with W warps (W = 16: one CTA per SM; W = 4: four per SM,
+// for layers with too few steps to feed 16-warp CTAs on every SM).
+__host__ __device__ constexpr int stream_bar_bytes(int w) { return w * kStages * 8; }
+__host__ __device__ constexpr int stream_ring_bytes(int w) { return w * kStages * kBlockBytes; }
+__host__ __device__ constexpr int stream_x_bytes(int w) { return w * 4096; }   // 64 KB / 16 KB
+__host__ __device__ constexpr int stream_smem_bytes(int w) {
+    return stream_bar_bytes(w) + stream_ring_bytes(w) + stream_x_bytes(w);
+}
 constexpr unsigned kStatusCopyTimeout = 1u;
 constexpr int kWaitLimit = 1 << 20;          // mbarrier polls before a warp gives up
 
@@ -52,14 +58,15 @@ struct StreamArgs {
     const __half* x;        // [M, K], row stride ldx
     const uint8_t* native;  // weight image
     __half* y;              // [M, N], row stride ldy
-    float* partial;         // [splits][n16][MT][32 lanes][4] when splits > 1
-    unsigned* ticket;       // [n16], zero on entry and on exit
+    float* partial;         // [split tile][max_parts][MT][32 lanes][4]
+    unsigned* ticket;       // [split tile], zero on entry and on exit
     unsigned* status;       // sticky error word (0 = ok)
     int64_t ldx, ldy;
     int m, n, k;
     int n16, kb;            // row tiles, column blocks
-    int kb_per_item;        // column blocks per K-split
-    int splits;
+    int groups;             // row groups = ceil(n16 / W)
+    int max_parts;          // partial slots per row tile
+    long long steps;        // groups * kb
 };
 
 // ---- small PTX helpers ------------------------------------------------------------------
@@ -79,12 +86,17 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1),
           "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
-__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0,
-                                         const float (&c)[4]) {
-    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 "
-        "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(b0), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+// fp32(lo half of h2) + c and fp32(hi half) + c: exact conversion plus add, one instruction each.
+__device__ __forceinline__ void add_mixed(uint32_t h2, float c, float& lo, float& hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "add.rn.f32.f16 %0, l, %3;\n\tadd.rn.f32.f16 %1, h, %3;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(h2), "f"(c));
+}
+// fp32(half) * (1/16) + c, exact (the product is an integer below 2^11).
+__device__ __forceinline__ void fma_mixed_16th(uint32_t h2, float c, float& lo, float& hi) {
+    asm("{\n\t.reg .b16 l, h, s;\n\tmov.b32 {l, h}, %2;\n\tmov.b16 s, 0x2C00;\n\t"
+        "fma.rn.f32.f16 %0, l, s, %3;\n\tfma.rn.f32.f16 %1, h, s, %3;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(h2), "f"(c));
 }
 // (lo*s, hi*s) rounded to an FP16 pair; each multiply is one IEEE FP32 rounding.
 __device__ __forceinline__ uint32_t scale_pack(float lo, float hi, float s) {
@@ -116,12 +128,6 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-struct BlockRegs {
-    uint4 code[4];   // piece j: rows g (j<2) / g+8 (j>=2), words 4*(j&1)..4*(j&1)+3
-    float2 step;     // (row g, row g+8)
-    uint32_t zero;   // zero(row g) | zero(row g+8) << 4
-};
-
 __device__ __forceinline__ uint32_t pick(const uint4& v, int i) {
     return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
 }
@@ -129,12 +135,13 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int i) {
 // Stage x[0..MT*8) x [k0, k0 + cols) into shared memory (zero beyond M and K).
 // Piece (row m, 64-column chunk T, 16-byte piece c) lands at ((T*MP + m)*8 + (c ^ key))*16
 // with key = ((m & 1) << 2) | (T & 3).
-template <int MT, bool XVEC>
+template <int MT, bool XVEC, int W>
 __device__ __forceinline__ void stage_x(uint4* xs, const StreamArgs& a, int k0, int cols) {
     constexpr int MP = MT * 8;
+    constexpr int kThreads = W * 32;
     const int pieces_per_row = cols >> 3;
     const int total = MP * pieces_per_row;
-    for (int i = threadIdx.x; i < total; i += 256) {
+    for (int i = threadIdx.x; i < total; i += kThreads) {
         const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
         const int T = cc >> 3, c = cc & 7;
         const int k = k0 + cc * 8;
@@ -156,119 +163,196 @@ __device__ __forceinline__ void stage_x(uint4* xs, const StreamArgs& a, int k0, 
     }
 }
 
+// Index of the CTA whose range contains step s (ranges are [c*steps/G, (c+1)*steps/G)).
+__device__ __forceinline__ int owner_of(long long s, long long steps, int ctas) {
+    return int(((s + 1) * ctas - 1) / steps);
+}
+
 // MT = number of 8-row tiles of x (1, 2, 4 or 8).  XVEC: x rows are 16-byte aligned and
 // K is a multiple of 8, so x is read with 16-byte loads.
-template <int MT, bool XVEC>
-__global__ void __launch_bounds__(256, 2)
+template <int MT, bool XVEC, int W>
+__global__ void __launch_bounds__(W * 32, (W == 16 ? 1 : 4))
 w4a16_stream_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MP = MT * 8;
-    constexpr int kPhaseCols = kXBytes / (MP * 2);       // 2048, 1024, 512, 256
+    constexpr int kWarps = W;
+    constexpr int kBarBytes = stream_bar_bytes(W), kRingBytes = stream_ring_bytes(W);
+    constexpr int kPhaseCols = stream_x_bytes(W) / (MP * 2);   // W=16: 4096, 2048, 1024, 512 columns
     constexpr int kPhaseBlocks = kPhaseCols / kBlockCols;
+    static_assert(kPhaseBlocks >= 1, "x phase must hold at least one column block");
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int nt = blockIdx.x * kWarps + warp;
-    const bool active = nt < a.n16;
-    const int ks = blockIdx.y;
-    const int kb0 = ks * a.kb_per_item;
-    const int kb1 = min(a.kb, kb0 + a.kb_per_item);
+    const int ctas = gridDim.x;
+    const long long b0 = (a.steps * blockIdx.x) / ctas;
+    const long long b1 = (a.steps * (blockIdx.x + 1)) / ctas;
+
+    // This warp's tile exists in every row group except possibly the last one.
+    const bool in_last = (a.groups - 1) * kWarps + warp < a.n16;
+    const long long last_start = (long long)(a.groups - 1) * a.kb;
+    const long long wb1 = in_last ? b1 : (b1 < last_start ? b1 : last_start);   // end of this warp's steps
 
     const uint32_t bar0 = smem_u32(smem) + warp * kStages * 8;
     uint8_t* ring = smem + kBarBytes + warp * kStages * kBlockBytes;
     const uint32_t ring0 = smem_u32(ring);
     uint4* xs = reinterpret_cast<uint4*>(smem + kBarBytes + kRingBytes);
 
-    const int64_t stride = int64_t(a.n16) * kBlockBytes;
-    const uint8_t* src = a.native + (int64_t(kb0) * a.n16 + (active ? nt : 0)) * kBlockBytes;
-
+    // Copy-request cursor (used by lane 0): image block (fkb, 16*fgrp + warp).  Consecutive
+    // column blocks of one row tile are `stride` bytes apart; at the end of a row group the
+    // cursor jumps to the first column block of the next group.
+    const long long stride = (long long)a.n16 * kBlockBytes;
+    long long fetch = b0;          // next step to request
+    int fgrp = int(b0 / a.kb);
+    int fkb = int(b0 - (long long)fgrp * a.kb);
+    const uint8_t* fptr = a.native + ((long long)fkb * a.n16 + fgrp * kWarps + warp) * kBlockBytes;
+    auto request = [&](int slot) {
+        mbar_expect_tx(bar0 + slot * 8, kBlockBytes);
+        bulk_copy_g2s(ring0 + slot * kBlockBytes, fptr, kBlockBytes, bar0 + slot * 8);
+        ++fetch;
+        fptr += stride;
+        if (++fkb == a.kb) {
+            fkb = 0;
+            ++fgrp;
+            fptr = a.native + (long long)(fgrp * kWarps + warp) * kBlockBytes;
+        }
+    };
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) mbar_init(bar0 + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        if (active) {
 #pragma unroll
-            for (int s = 0; s < kStages; ++s)
-                if (kb0 + s < kb1) {
-                    mbar_expect_tx(bar0 + s * 8, kBlockBytes);
-                    bulk_copy_g2s(ring0 + s * kBlockBytes, src + s * stride, kBlockBytes, bar0 + s * 8);
-                }
-        }
+        for (int s = 0; s < kStages; ++s)
+            if (fetch < wb1) request(s);
     }
     __syncwarp();
 
-    // selection matrices of the conversion MMAs, as B fragments of this lane
-    const uint32_t sel1 = (2 * t == g) ? 0x00003C00u : (2 * t + 1 == g) ? 0x3C000000u : 0u;  // 1.0
-    const uint32_t sel16 = (2 * t == g) ? 0x00002C00u : (2 * t + 1 == g) ? 0x2C000000u : 0u; // 1/16
     const int xkey = ((g & 1) << 2) | t;
-
     float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
-
     int stage = 0;
     uint32_t parity = 0;
     bool failed = false;
 
-    for (int p0 = kb0; p0 < kb1; p0 += kPhaseBlocks) {
-        __syncthreads();                                   // everyone is done with the previous phase's x
-        stage_x<MT, XVEC>(xs, a, p0 * kBlockCols, min(kPhaseBlocks, kb1 - p0) * kBlockCols);
-        __syncthreads();
-        if (!active || failed) continue;
-        const int p1 = min(kb1, p0 + kPhaseBlocks);
-        for (int kb = p0; kb < p1; ++kb) {
-            if (!mbar_wait(bar0 + stage * 8, parity)) {
-                failed = true;
-                if (lane == 0) atomicOr(a.status, kStatusCopyTimeout);
-                break;
-            }
-            const uint8_t* slot = ring + stage * kBlockBytes;
-            BlockRegs cur;
+    long long s0 = b0;
+    while (s0 < b1) {                                       // one iteration per row group in the range
+        const int grp = int(s0 / a.kb);
+        const int k_lo = int(s0 - (long long)grp * a.kb);
+        const int k_hi = int(min((long long)a.kb, k_lo + (b1 - s0)));
+        const int nt = grp * kWarps + warp;
+        const bool active = nt < a.n16;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) cur.code[j] = *reinterpret_cast<const uint4*>(slot + j * 512 + lane * 16);
-            cur.step = *reinterpret_cast<const float2*>(slot + kStepOffset + lane * 8);
-            cur.zero = slot[kZeroOffset + lane];
-            __syncwarp();                                  // all lanes have read the slot
-            if (lane == 0 && kb + kStages < kb1) {
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_expect_tx(bar0 + stage * 8, kBlockBytes);
-                bulk_copy_g2s(ring0 + stage * kBlockBytes, src + int64_t(kb - kb0 + kStages) * stride,
-                              kBlockBytes, bar0 + stage * 8);
-            }
-            if (++stage == kStages) { stage = 0; parity ^= 1u; }
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
 
-            const float zg = float(cur.zero & 15u), zh = float(cur.zero >> 4);
-            const float c1[4] = {-(1024.0f + zg), -(1024.0f + zg), -(1024.0f + zh), -(1024.0f + zh)};
-            const float c2[4] = {-(64.0f + zg), -(64.0f + zg), -(64.0f + zh), -(64.0f + zh)};
-            const float sg = cur.step.x, sh = cur.step.y;
-            const uint4* xchunk = xs + ((kb - p0) * 4 + t) * (MP * 8) + g * 8;
+        for (int p0 = k_lo; p0 < k_hi; p0 += kPhaseBlocks) {
+            const int p1 = min(k_hi, p0 + kPhaseBlocks);
+            __syncthreads();                               // everyone is done with the previous x phase
+            stage_x<MT, XVEC, W>(xs, a, p0 * kBlockCols, (p1 - p0) * kBlockCols);
+            __syncthreads();
+            if (!active || failed) continue;
+            for (int kb = p0; kb < p1; ++kb) {
+                if (!mbar_wait(bar0 + stage * 8, parity)) {
+                    failed = true;
+                    if (lane == 0) atomicOr(a.status, kStatusCopyTimeout);
+                    break;
+                }
+                const uint8_t* slot = ring + stage * kBlockBytes;
+                uint4 code[4];
 #pragma unroll
-            for (int wi = 0; wi < 8; ++wi) {
-                const uint32_t wa = pick(cur.code[wi >> 2], wi & 3);        // row g
-                const uint32_t wb = pick(cur.code[2 + (wi >> 2)], wi & 3);  // row g+8
-                uint4 xv[MT];
+                for (int j = 0; j < 4; ++j) code[j] = *reinterpret_cast<const uint4*>(slot + j * 512 + lane * 16);
+                const float2 step = *reinterpret_cast<const float2*>(slot + kStepOffset + lane * 8);
+                const uint32_t zero = slot[kZeroOffset + lane];
+                __syncwarp();                              // all lanes have read the slot
+                if (lane == 0 && fetch < wb1) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    request(stage);
+                }
+                if (++stage == kStages) { stage = 0; parity ^= 1u; }
+
+                const float zg = float(zero & 15u), zh = float(zero >> 4);
+                const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);   // even nibbles: (1024+q) - (1024+z)
+                const float eg = -(64.0f + zg), eh = -(64.0f + zh);       // odd nibbles: (1024+16q)/16 - (64+z)
+                const float sg = step.x, sh = step.y;
+                const uint4* xchunk = xs + ((kb - p0) * 4 + t) * (MP * 8) + g * 8;
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) xv[mt] = xchunk[mt * 64 + (wi ^ xkey)];
+                for (int wi = 0; wi < 8; ++wi) {
+                    const uint32_t wa = pick(code[wi >> 2], wi & 3);        // row g
+                    const uint32_t wb = pick(code[2 + (wi >> 2)], wi & 3);  // row g+8
+                    uint4 xv[MT];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
-                    float d1[4], d2[4];
-                    mma_1688(d1, and_or(ua, 0x000F000Fu, 0x64006400u), and_or(ub, 0x000F000Fu, 0x64006400u),
-                             sel1, c1);                     // columns 0,1 of the quad: code - zero
-                    mma_1688(d2, and_or(ua, 0x00F000F0u, 0x64006400u), and_or(ub, 0x00F000F0u, 0x64006400u),
-                             sel16, c2);                    // columns 2,3
-                    const uint32_t w[4] = {scale_pack(d1[0], d1[1], sg), scale_pack(d1[2], d1[3], sh),
-                                           scale_pack(d2[0], d2[1], sg), scale_pack(d2[2], d2[3], sh)};
+                    for (int mt = 0; mt < MT; ++mt) xv[mt] = xchunk[mt * 64 + (wi ^ xkey)];
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
-                        mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
+                    for (int e = 0; e < 2; ++e) {
+                        const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
+                        float d[8];
+                        add_mixed(and_or(ua, 0x000F000Fu, 0x64006400u), cg, d[0], d[1]);
+                        add_mixed(and_or(ub, 0x000F000Fu, 0x64006400u), ch, d[2], d[3]);
+                        fma_mixed_16th(and_or(ua, 0x00F000F0u, 0x64006400u), eg, d[4], d[5]);
+                        fma_mixed_16th(and_or(ub, 0x00F000F0u, 0x64006400u), eh, d[6], d[7]);
+                        const uint32_t w[4] = {scale_pack(d[0], d[1], sg), scale_pack(d[2], d[3], sh),
+                                               scale_pack(d[4], d[5], sg), scale_pack(d[6], d[7], sh)};
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+                            mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
+                    }
                 }
             }
         }
+
+        if (active && !failed) {
+            const bool whole = (k_lo == 0 && k_hi == a.kb);
+            bool write_out = whole;
+            if (!whole) {
+                // Contributors to this row group are the CTAs first..last; mine is slot `blockIdx.x - first`.
+                const long long gs = (long long)grp * a.kb;
+                const int first = owner_of(gs, a.steps, ctas), last = owner_of(gs + a.kb - 1, a.steps, ctas);
+                const int parts = last - first + 1;
+                // Row groups that are split between CTAs are few: at most one per CTA boundary.
+                // Both `grp` and `first` are unique among them; use whichever range is smaller.
+                const int tile = (a.groups <= ctas ? grp : first) * kWarps + warp;
+                float4* base = reinterpret_cast<float4*>(a.partial) + (long long)tile * a.max_parts * (MT * 32) + lane;
+                float4* mine = base + (long long)(blockIdx.x - first) * (MT * 32);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                    __stcg(mine + mt * 32, make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]));
+                __threadfence();
+                __syncwarp();
+                unsigned prior = 0;
+                if (lane == 0) prior = atomicAdd(a.ticket + tile, 1u);
+                prior = __shfl_sync(0xffffffffu, prior, 0);
+                if (prior == unsigned(parts - 1)) {
+                    __threadfence();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
+                    for (int s = 0; s < parts; ++s) {
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const float4 p = __ldcg(base + (long long)s * (MT * 32) + mt * 32);
+                            acc[mt][0] += p.x; acc[mt][1] += p.y; acc[mt][2] += p.z; acc[mt][3] += p.w;
+                        }
+                    }
+                    if (lane == 0) a.ticket[tile] = 0u;
+                    write_out = true;
+                }
+            }
+            if (write_out) {
+                const int n0 = nt * 16 + g;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int m0 = mt * 8 + 2 * t;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int m = m0 + (c & 1), n = n0 + 8 * (c >> 1);
+                        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = __float2half_rn(acc[mt][c]);
+                    }
+                }
+            }
+        }
+        s0 += k_hi - k_lo;
     }
-    if (!active) return;
+
     if (failed) {
         // Let copies that are still in flight land before the CTA's shared memory is released.
         for (int s = 0; s < kStages; ++s) {
@@ -276,46 +360,6 @@ w4a16_stream_kernel(const StreamArgs a) {
             for (int i = 0; i < 4096 && !landed; ++i) landed = mbar_try_wait(bar0 + stage * 8, parity);
             if (!landed) break;
             if (++stage == kStages) { stage = 0; parity ^= 1u; }
-        }
-        return;
-    }
-
-    const int n0 = nt * 16 + g;
-    if (a.splits > 1) {
-        float4* mine = reinterpret_cast<float4*>(a.partial) + (int64_t(ks) * a.n16 + nt) * (MT * 32) + lane;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-            __stcg(mine + mt * 32, make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]));
-        __threadfence();
-        __syncwarp();
-        unsigned prior = 0;
-        if (lane == 0) prior = atomicAdd(a.ticket + nt, 1u);
-        prior = __shfl_sync(0xffffffffu, prior, 0);
-        if (prior != unsigned(a.splits - 1)) return;
-        __threadfence();
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
-        const float4* part = reinterpret_cast<const float4*>(a.partial) + int64_t(nt) * (MT * 32) + lane;
-        for (int s = 0; s < a.splits; ++s) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const float4 p = __ldcg(part + mt * 32);
-                acc[mt][0] += p.x; acc[mt][1] += p.y; acc[mt][2] += p.z; acc[mt][3] += p.w;
-            }
-            part += int64_t(a.n16) * (MT * 32);
-        }
-        if (lane == 0) a.ticket[nt] = 0u;
-    }
-
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        const int m0 = mt * 8 + 2 * t;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int m = m0 + (c & 1), n = n0 + 8 * (c >> 1);
-            if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = __float2half_rn(acc[mt][c]);
         }
     }
 }

@@ -249,7 +249,8 @@ def test_linearity_and_full_size_property():
     x = torch.randn(16, k, generator=g).half().cuda()
     y = layer(x)
     assert torch.count_nonzero(layer(torch.zeros_like(x))) == 0
-    assert torch.equal(layer(x * 2), y * 2)
+    normal = y.abs() >= 2.0 ** -13          # doubling is exact only above the FP16 subnormal range
+    assert torch.equal(layer(x * 2)[normal], (y * 2)[normal])
     w16 = layer.dequantize().half()
     expected = (x.double() @ w16.double().t())
     assert (y.double() - expected).abs().max() <= 2e-3 + 2e-3 * expected.abs().max()
