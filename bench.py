@@ -1,0 +1,447 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 quantized-linear engine.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line.  A "step" is one pass of the hot path over one batch of synthetic
+input: every projection of the workload at every batch size M, over enough distinct
+layers that the weights of a step (>= 250 MB) cannot stay in the 126 MB L2.
+
+  metric  weight-HBM GB/s = algorithmic weight bytes (N*K/2 + N*ceil(K/64)*4.5 per layer)
+          streamed per second, whole job (all ranks)
+  value   device-resident inputs, the step replayed as one CUDA graph, CUDA events
+  e2e     the same step through the public operator (QuantizedLinear.forward, eager) with
+          x copied from pinned host memory and y copied back for every call
+  roofline, cpu_baseline, clocks, gpu_launches: see the keys' comments below
+
+Workloads (shapes are N x K of synthetic projections, weights ~ N(0, sigma^2) quantized
+by QuantizedLinear.from_float(group_size=64), x ~ N(0,1) FP16):
+  qwen3-0.6b-decode  28 layers x {4096x1024, 1024x2048, 6144x1024, 1024x3072}, M in 1,2,4,8
+  qwen3-8b-layer      3 layers x {6144x4096, 4096x4096, 24576x4096, 4096x12288}, M in 1,16
+  llama3-70b-mlp      1 layer  x {57344x8192, 8192x28672}, M in 1,8, rows sharded over ranks
+
+With N > 1 (launched under torchrun, one rank per GPU) the first two workloads run one
+replica of the projection set per rank (weak scaling: rank r owns rows [r*N,(r+1)*N) of a
+P-times wider layer, no exchange); llama3-70b-mlp splits each layer's rows over the ranks
+(strong scaling) and `--gather` adds the NCCL all-gather of the output slices.
+
+`--impl reference` times the CPU restatement of the reference's own CPU route (the oracle,
+torch FP32 matmul on all host threads) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT), str(ROOT / "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch
+
+WORKLOADS = {
+    "qwen3-0.6b-decode": {"shapes": [("qkv", 4096, 1024), ("o", 1024, 2048), ("gate_up", 6144, 1024),
+                                     ("down", 1024, 3072)],
+                          "layers": 28, "ms": [1, 2, 4, 8], "sigma": 0.02, "seed": 1000, "shard": False},
+    "qwen3-8b-layer": {"shapes": [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096),
+                                  ("down", 4096, 12288)],
+                       "layers": 3, "ms": [1, 16], "sigma": 0.02, "seed": 2000, "shard": False},
+    "llama3-70b-mlp": {"shapes": [("gate_up", 57344, 8192), ("down", 8192, 28672)],
+                       "layers": 1, "ms": [1, 8], "sigma": 0.015, "seed": 3000, "shard": True},
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def weight_bytes(n, k):
+    """Algorithmic weight bytes of one layer: 4-bit codes + FP32 step + 4-bit zero point per group."""
+    return n * k / 2 + n * ((k + 63) // 64) * 4.5
+
+
+def io_bytes(m, n, k):
+    return 2 * m * k + 2 * m * n
+
+
+def measured_hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            reasons.update(n for n, v in zip(names, parts[2:]) if v == "Active")
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# workload construction
+# ----------------------------------------------------------------------------------------------
+def build_layers(spec, rank, world, device):
+    """[(name, n_local, k, layer)] per layer index; weights are seeded per (layer, shape, rank)."""
+    import dandan_ops_b200 as ops
+    from dandan_ops_b200.sharded import shard_rows
+
+    out = []
+    for li in range(spec["layers"]):
+        row = []
+        for si, (name, n, k) in enumerate(spec["shapes"]):
+            gen = torch.Generator(device=device)
+            gen.manual_seed(spec["seed"] + 100 * li + si + 7919 * rank)   # a stream per (layer, shape, rank)
+            rows = n
+            if spec["shard"]:
+                start, stop = shard_rows(n, world, rank)
+                rows = stop - start
+            if rows == 0:
+                row.append((name, 0, k, None))
+                continue
+            w = (torch.randn(rows, k, generator=gen, device=device) * spec["sigma"]).half()
+            row.append((name, rows, k, ops.QuantizedLinear.from_float(w, group_size=64)))
+            del w
+        out.append(row)
+    return out
+
+
+def make_inputs(spec, device, pinned=False):
+    xs = {}
+    gen = torch.Generator().manual_seed(spec["seed"] + 5)
+    for m in spec["ms"]:
+        for k in sorted({k for _, _, k in spec["shapes"]}):
+            x = torch.randn(m, k, generator=gen).half()
+            xs[(m, k)] = x.pin_memory() if pinned else x.to(device)
+    return xs
+
+
+def run_gpu(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from dandan_ops_b200 import _native
+
+    spec = WORKLOADS[args.workload]
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _native.load()
+
+    layers = build_layers(spec, rank, world, device)
+    x_dev = make_inputs(spec, device)
+    x_host = make_inputs(spec, device, pinned=True)
+    calls = [(m, name, n, k, layer) for m in spec["ms"] for row in layers for (name, n, k, layer) in row
+             if layer is not None]
+    step_weight_bytes = sum(weight_bytes(n, k) for _, _, n, k, _ in calls)
+    step_alg_bytes = step_weight_bytes + sum(io_bytes(m, n, k) for m, _, n, k, _ in calls)
+    native_resident = sum(layer.native_bytes for row in layers for (_, _, _, layer) in row if layer is not None)
+
+    gather_layers = None
+    if args.gather and spec["shard"] and world > 1:
+        from dandan_ops_b200.sharded import ColumnShardedLinear
+        gather_layers = {id(layer): ColumnShardedLinear(layer, out_features=n_full, rank=rank, world_size=world)
+                         for row in layers for ((name, n, k, layer), (_, n_full, _)) in zip(row, spec["shapes"])
+                         if layer is not None}
+
+    def one_step():
+        outs = None
+        for m, _, n, k, layer in calls:
+            y = layer(x_dev[(m, k)])
+            if gather_layers is not None:
+                y = gather_layers[id(layer)].gather(y)
+            outs = y
+        return outs
+
+    stream = torch.cuda.Stream(device)
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        before = _native.launch_count()
+        one_step()
+        launches_per_step = _native.launch_count() - before
+        for _ in range(2):
+            one_step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        use_graph = gather_layers is None
+        if use_graph:
+            with torch.cuda.graph(graph, stream=stream):
+                one_step()
+            replay = graph.replay
+        else:
+            replay = one_step
+
+        def sync_all():
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(max(args.warmup, 3)):
+            replay()
+        sync_all()
+        with ClockSampler(local_rank) as clocks:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                replay()
+            e1.record(stream)
+            sync_all()
+        gpu_ms = e0.elapsed_time(e1)
+
+        # end to end: pinned host x -> device, eager public API call, y -> pinned host, every call
+        y_host = {(m, n): torch.empty((m, n), dtype=torch.float16).pin_memory() for m, _, n, _, _ in calls}
+        x_stage = {key: torch.empty_like(v, device=device) for key, v in x_host.items()}
+
+        def e2e_step():
+            for m, _, n, k, layer in calls:
+                x_stage[(m, k)].copy_(x_host[(m, k)], non_blocking=True)
+                y = layer(x_stage[(m, k)])
+                y_host[(m, n)].copy_(y, non_blocking=True)
+
+        e2e_steps = max(1, min(args.steps, 5))
+        e2e_step()
+        sync_all()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        t1.record(stream)
+        sync_all()
+        e2e_ms = t0.elapsed_time(t1)
+
+    times = torch.tensor([gpu_ms / args.steps, e2e_ms / e2e_steps], dtype=torch.float64, device=device)
+    bytes_all = torch.tensor([step_weight_bytes, step_alg_bytes], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(bytes_all, op=dist.ReduceOp.SUM)
+    ms_per_step, e2e_ms_per_step = (float(v) for v in times.cpu())
+    weight_total, alg_total = (float(v) for v in bytes_all.cpu())
+
+    detail = per_shape_detail(spec, layers, x_dev, stream) if (rank == 0 and not args.no_detail) else None
+    cpu = cpu_baseline(spec, sample_seconds=args.cpu_seconds) if (rank == 0 and world == 1 and not args.no_cpu) else None
+
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        # per launch: one rank's algorithmic bytes of a step / its launches, over the average launch time
+        launches = launches_per_step
+        achieved = (step_alg_bytes / launches) / (ms_per_step * 1e-3 / launches) / 1e9
+        result = {
+            "metric": "w4a16_decode_weight_hbm_GBps", "value": round(weight_total / (ms_per_step * 1e-3) / 1e9, 2),
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None,
+            "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "layers": spec["layers"], "batch_sizes": spec["ms"],
+                       "shapes_NxK": [f"{n}x{k}" for _, n, k in spec["shapes"]],
+                       "linears_per_step": len(calls), "weight_bytes_per_step_per_gpu": int(step_weight_bytes),
+                       "native_image_bytes_resident_per_gpu": int(native_resident),
+                       "cache": "weights of a step exceed L2 (inputs larger than L2, no flush)",
+                       "timing": "step replayed as one CUDA graph" if use_graph else "eager launches",
+                       "gather": bool(gather_layers)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "w4a16_stream_kernel",
+                         "note": "achieved = algorithmic bytes per launch / average launch time over the graph"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": round(weight_total / (e2e_ms_per_step * 1e-3) / 1e9, 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": int(sum(2 * m * k for m, _, _, k, _ in calls)),
+                    "d2h_bytes_per_step": int(sum(2 * m * n for m, _, n, _, _ in calls)),
+                    "ms_per_step": round(e2e_ms_per_step, 4)},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "clocks": clocks.summary(),
+            "detail": detail,
+        }
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def per_shape_detail(spec, layers, x_dev, stream):
+    """Median CUDA-graph replay time of every (projection, M): microseconds, weight GB/s, TFLOPS.
+    Each graph walks all layers of the workload, so consecutive launches never reuse weights."""
+    out = []
+    with torch.cuda.stream(stream):
+        for si, (name, n_full, k) in enumerate(spec["shapes"]):
+            column = [row[si] for row in layers if row[si][3] is not None]
+            if not column:
+                continue
+            n = column[0][1]
+            reps = max(1, int(300e6 // max(1.0, len(column) * weight_bytes(n, k))))
+            for m in spec["ms"]:
+                x = x_dev[(m, k)]
+                for _, _, _, layer in column:
+                    layer(x)
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for _ in range(reps):
+                        for _, _, _, layer in column:
+                            layer(x)
+                samples = []
+                for _ in range(7):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    graph.replay()
+                    e1.record(stream)
+                    stream.synchronize()
+                    samples.append(e0.elapsed_time(e1) * 1e3 / (reps * len(column)))
+                us = statistics.median(samples)
+                out.append({"proj": name, "N": n, "K": k, "M": m, "us": round(us, 2),
+                            "weight_GBps": round(weight_bytes(n, k) / us / 1e3, 1),
+                            "TFLOPS": round(2.0 * m * n * k / us / 1e6, 2)})
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the oracle's restatement of the reference's CPU route
+# ----------------------------------------------------------------------------------------------
+def cpu_state(n, k, sigma, seed):
+    from oracle import w4a16_oracle as oracle
+
+    gen = torch.Generator().manual_seed(seed)
+    w = (torch.randn(n, k, generator=gen) * sigma).half()
+    codes, step, zero = oracle.quantize(w.numpy())
+    return torch.from_numpy(oracle.pack(codes)), torch.from_numpy(step), torch.from_numpy(zero)
+
+
+def cpu_pass(spec, states, xs):
+    """One pass over one layer's projections at every M on the host.  Returns weight bytes covered."""
+    from oracle import w4a16_oracle as oracle
+
+    covered = 0.0
+    for (name, n, k), (words, step, zero) in zip(spec["shapes"], states):
+        for m in spec["ms"]:
+            oracle.torch_forward(xs[(m, k)], words, step, zero, k)
+            covered += weight_bytes(n, k)
+    return covered
+
+
+def cpu_baseline(spec, sample_seconds=15.0):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    shapes = spec["shapes"]
+    if max(n * k for _, n, k in shapes) > 200e6:      # bound the sample: quarter-height slices of huge layers
+        shapes = [(name, n // 8, k) for name, n, k in shapes]
+    small = dict(spec, shapes=shapes)
+    states = [cpu_state(n, k, spec["sigma"], spec["seed"] + i) for i, (_, n, k) in enumerate(shapes)]
+    gen = torch.Generator().manual_seed(spec["seed"] + 5)
+    xs = {(m, k): torch.randn(m, k, generator=gen).half() for m in spec["ms"] for k in {k for _, _, k in shapes}}
+    cpu_pass(small, states, xs)                        # warm-up
+    covered, t0, passes = 0.0, time.perf_counter(), 0
+    while passes < 1 or (time.perf_counter() - t0 < sample_seconds and passes < 50):
+        covered += cpu_pass(small, states, xs)
+        passes += 1
+    elapsed = time.perf_counter() - t0
+    return {"value": round(covered / elapsed / 1e9, 4), "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{passes} passes over one layer's projections {[f'{n}x{k}' for _, n, k in shapes]} "
+                      f"at M={spec['ms']} ({elapsed:.1f} s, torch FP32 matmul restatement of the reference CPU route)"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    spec = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    shapes = spec["shapes"]
+    if max(n * k for _, n, k in shapes) > 200e6:
+        shapes = [(name, n // 8, k) for name, n, k in shapes]
+    small = dict(spec, shapes=shapes)
+    states = [cpu_state(n, k, spec["sigma"], spec["seed"] + i) for i, (_, n, k) in enumerate(shapes)]
+    gen = torch.Generator().manual_seed(spec["seed"] + 5)
+    xs = {(m, k): torch.randn(m, k, generator=gen).half() for m in spec["ms"] for k in {k for _, _, k in shapes}}
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_pass(small, states, xs)
+    t0 = time.perf_counter()
+    covered = 0.0
+    for _ in range(args.steps):
+        covered += cpu_pass(small, states, xs)
+    elapsed = time.perf_counter() - t0
+    value = round(covered / elapsed / 1e9, 4)
+    sample = (f"each step = one layer's projections {[f'{n}x{k}' for _, n, k in shapes]} at M={spec['ms']} "
+              f"on {cores} host threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "w4a16_decode_weight_hbm_GBps", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(elapsed / args.steps * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None,
+        "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "batch_sizes": spec["ms"],
+                   "shapes_NxK": [f"{n}x{k}" for _, n, k in shapes]},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen3-0.6b-decode")
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--gather", action="store_true", help="all-gather output slices (sharded workload, N>1)")
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-shape table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus and args.gpus > 1:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the package has no CPU compute path")
+    run_gpu(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
