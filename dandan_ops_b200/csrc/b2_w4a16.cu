@@ -11,6 +11,7 @@
 #include "layout.cuh"
 #include "layout_kernels.cuh"
 #include "stream_kernel.cuh"
+#include "gemm_kernel.cuh"
 
 namespace {
 
@@ -171,6 +172,75 @@ int64_t stream_workspace_bytes(int64_t m, const b2::Dims& d, int sm_count) {
     return B2_W4A16_TICKET_BYTES + p.partial_bytes;
 }
 
+// ---------------------------------------------------------------------------------------
+// tcgen05 GEMM: tensor map for x and launch.
+// ---------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static std::atomic<EncodeTiledFn> cached{nullptr};
+    EncodeTiledFn fn = cached.load(std::memory_order_acquire);
+    if (fn) return fn;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) != cudaSuccess ||
+        status != cudaDriverEntryPointSuccess || ptr == nullptr)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    cached.store(fn, std::memory_order_release);
+    return fn;
+}
+
+bool gemm_applicable(const void* x, int64_t ldx, const b2::Dims& d) {
+    return reinterpret_cast<uintptr_t>(x) % 16 == 0 && ldx % 8 == 0 && d.k % 8 == 0;
+}
+
+template <int MA, bool VEC>
+int launch_gemm_one(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_gemm_kernel<MA, VEC>;
+    constexpr int smem = b2::gemm_smem_bytes(MA);
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<grid, b2::kGemmThreads, smem, s>>>(map, a);
+    return after_launch("w4a16_gemm_kernel");
+}
+
+int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
+             const b2::Dims& d, void* workspace, cudaStream_t s) {
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return fail(B2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
+    if (workspace == nullptr) return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(m)};
+    const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(b2::kGemmBK), 128};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+    b2::GemmArgs a;
+    a.native = static_cast<const uint8_t*>(native);
+    a.y = static_cast<__half*>(y);
+    a.status = static_cast<unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1);
+    a.ldy = ldy;
+    a.m = int(m); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
+    const int ma = m <= 128 ? 1 : 2;
+    const dim3 grid((d.n + b2::kGemmBN - 1) / b2::kGemmBN, unsigned((m + 128 * ma - 1) / (128 * ma)));
+    const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
+    if (ma == 1) return vec ? launch_gemm_one<1, true>(map, a, grid, s) : launch_gemm_one<1, false>(map, a, grid, s);
+    return vec ? launch_gemm_one<2, true>(map, a, grid, s) : launch_gemm_one<2, false>(map, a, grid, s);
+}
+
 }  // namespace
 
 extern "C" {
@@ -247,6 +317,14 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
     if (device_info(dev) != B2_OK) dev.sm_count = 148;   // planning also works without a device
     const b2::Dims d = b2::make_dims(n, k);
     const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
+    if (m > B2_STREAM_MAX_M && d.k % 8 == 0) {     // assuming an aligned x, as execution_info cannot see the pointer
+        const int ma = m <= 128 ? 1 : 2;
+        if (route) *route = B2_ROUTE_TCGEN05;
+        if (k_splits) *k_splits = 1;
+        if (grid) *grid = ((d.n + b2::kGemmBN - 1) / b2::kGemmBN) * int((m + 128 * ma - 1) / (128 * ma));
+        if (rows_per_launch) *rows_per_launch = int(m);
+        return B2_OK;
+    }
     if (route) *route = B2_ROUTE_STREAM;
     if (k_splits) *k_splits = p.max_parts;
     if (grid) *grid = p.grid;
@@ -290,11 +368,19 @@ int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* 
     if (int rc = device_info(dev)) return rc;
     if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     const b2::Dims d = b2::make_dims(n, k);
-    if (route == B2_ROUTE_AUTO) route = B2_ROUTE_STREAM;
+    if (route == B2_ROUTE_AUTO)
+        route = (m > B2_STREAM_MAX_M && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
                           static_cast<cudaStream_t>(stream), dev);
-    return fail(B2_ERR_UNSUPPORTED, "unknown or unavailable route");
+    if (route == B2_ROUTE_TCGEN05) {
+        if (!gemm_applicable(x, ldx, d))
+            return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
+        if (workspace_bytes < B2_W4A16_TICKET_BYTES)
+            return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
+        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, static_cast<cudaStream_t>(stream));
+    }
+    return fail(B2_ERR_UNSUPPORTED, "unknown route");
 }
 
 int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,

@@ -256,3 +256,69 @@ def test_linearity_and_full_size_property():
     assert (y.double() - expected).abs().max() <= 2e-3 + 2e-3 * expected.abs().max()
     for m in (1, 2, 4, 8):
         assert (layer(x[:m]).double() - expected[:m]).abs().max() <= 4e-3
+
+
+# ------------------------------------------------------------------------------------------
+# tensor-memory GEMM route (M > 64 rows of x)
+# ------------------------------------------------------------------------------------------
+GEMM_SHAPES = [(65, 5, 8), (100, 1000, 1024), (128, 128, 64), (129, 127, 264), (256, 128, 512), (300, 12289, 1024),
+               (512, 192, 1024), (1000, 4096, 3072), (2048, 1024, 4096)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_tcgen05_route_against_oracle_formula(m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    layer = ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.05).half().cuda())
+    x = torch.randn(m, k, generator=g).half().cuda()
+    assert layer.execution_info(x)["implementation"] == "b200_tcgen05"
+    y = layer(x)
+    forced = _native.linear(x, layer._native_image(), n, k, route=_native.ROUTE_TCGEN05)
+    assert torch.equal(y, forced)
+    assert _native.status() == 0
+    expected = (x.double() @ layer.dequantize().half().double().t())
+    err = (y.double() - expected).abs()
+    assert bool((err <= ATOL + RTOL * expected.abs()).all())
+    # both kernel families must agree within the same tolerance
+    stream = _native.linear(x, layer._native_image(), n, k, route=_native.ROUTE_STREAM)
+    torch.testing.assert_close(y, stream, atol=ATOL, rtol=RTOL)
+    if m * n <= 400000:
+        assert_close_ref(y, oracle_y(x, layer))
+
+
+@pytest.mark.parametrize("n,k", [(37, 264), (1000, 1024), (130, 128)])
+def test_tcgen05_internal_weights_bit_exact(n, k):
+    """One-hot rows of x through the tensor-memory GEMM return the FP16 weights exactly."""
+    words, step, zero = cases.direct_state(n, k, n + 3 * k, lambda c: ops.pack_int4(c.cuda()))
+    for layer in (ops.QuantizedLinear(words, step.cuda(), zero.cuda(), in_features=k),
+                  ops.QuantizedLinear.from_float((torch.randn(n, k) * 0.02).cuda())):
+        want = oracle.dequantize_fp16(layer.packed_weight.cpu().numpy(), layer.scales.cpu().numpy(),
+                                      layer.zeros.cpu().numpy(), k)
+        eye = torch.eye(k, dtype=torch.float16, device="cuda")
+        y = _native.linear(eye, layer._native_image(), n, k, route=_native.ROUTE_TCGEN05)
+        got = y.t().contiguous().cpu().numpy()
+        assert np.array_equal(got, want) and np.isfinite(got).all()
+
+
+def test_tcgen05_unaligned_falls_back_and_graph_replay():
+    torch.manual_seed(9)
+    layer = ops.QuantizedLinear.from_float(torch.randn(200, 129, dtype=torch.float16).cuda())
+    x = torch.randn(100, 129, dtype=torch.float16).cuda()          # K % 8 != 0: streaming kernel
+    assert_close_ref(layer(x), oracle_y(x, layer))
+    with pytest.raises(RuntimeError, match="tcgen05"):
+        _native.linear(x, layer._native_image(), 200, 129, route=_native.ROUTE_TCGEN05)
+    layer = ops.QuantizedLinear.from_float(torch.randn(384, 512, dtype=torch.float16).cuda())
+    x = torch.randn(300, 512, dtype=torch.float16).cuda()
+    expected = oracle_y(x, layer)
+    for _ in range(3):
+        layer(x)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = layer(x)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert_close_ref(out, expected)
+    x.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(out) == 0
