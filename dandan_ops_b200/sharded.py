@@ -95,8 +95,9 @@ class ColumnShardedLinear(torch.nn.Module):
         pad = self.rows_per_rank - y_local.shape[1]
         piece = y_local if pad == 0 else torch.nn.functional.pad(y_local, (0, pad))
         piece = piece.contiguous()
-        out = piece.new_empty((self.world_size, m, self.rows_per_rank))
+        out = piece.new_empty((self.world_size * m, self.rows_per_rank))     # rank-major concatenation
         dist.all_gather_into_tensor(out, piece, group=self.process_group)
+        out = out.view(self.world_size, m, self.rows_per_rank)
         if m == 1:
             full = out.view(1, self.world_size * self.rows_per_rank)
         else:
