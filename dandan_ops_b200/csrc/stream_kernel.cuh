@@ -22,8 +22,8 @@
 // 16-byte shared loads and immediately hands the slot back to the copy engine.
 //
 // Activations: x for a phase of up to 4096 columns is staged in shared memory once per
-// CTA, laid out [64-column chunk][row][eight 16-byte pieces, XOR-swizzled] so that the
-// 16-byte read a lane makes for its MMA B fragments is conflict-free.
+// CTA, laid out [64-column chunk][row][eight 16-byte pieces] with padded rows and chunks so
+// that the 16-byte read a lane makes for its MMA B fragments is conflict-free.
 //
 // Dequantization keeps the reference's arithmetic exactly:
 //     w = fp16_rn( fp32(code - zero) * step_fp32 )
@@ -47,7 +47,11 @@ constexpr int kStages = 4;                   // ring depth per warp
 // for layers with too few steps to feed 16-warp CTAs on every SM).
 __host__ __device__ constexpr int stream_bar_bytes(int w) { return w * kStages * 8; }
 __host__ __device__ constexpr int stream_ring_bytes(int w) { return w * kStages * kBlockBytes; }
-__host__ __device__ constexpr int stream_x_bytes(int w) { return w * 4096; }   // 64 KB / 16 KB
+__host__ __device__ constexpr int stream_x_bytes(int w) { return w * 4736; }   // 74 KB / 18.5 KB
+// Staged x: 64-column chunk T, row m, 16-byte piece c at T*chunk + m*144 + c*16.  Rows are padded
+// to 144 bytes and chunks by 32 more, which spreads the eight lanes of a quarter warp (two rows x
+// four chunks) over all eight 16-byte bank groups without any address arithmetic per piece.
+__host__ __device__ constexpr int stream_x_chunk_bytes(int rows) { return rows * 144 + 32; }
 __host__ __device__ constexpr int stream_smem_bytes(int w) {
     return stream_bar_bytes(w) + stream_ring_bytes(w) + stream_x_bytes(w);
 }
@@ -133,10 +137,8 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int i) {
 }
 
 // Stage x[0..MT*8) x [k0, k0 + cols) into shared memory (zero beyond M and K).
-// Piece (row m, 64-column chunk T, 16-byte piece c) lands at ((T*MP + m)*8 + (c ^ key))*16
-// with key = ((m & 1) << 2) | (T & 3).
 template <int MT, bool XVEC, int W>
-__device__ __forceinline__ void stage_x(uint4* xs, const StreamArgs& a, int k0, int cols) {
+__device__ __forceinline__ void stage_x(uint8_t* xs, const StreamArgs& a, int k0, int cols) {
     constexpr int MP = MT * 8;
     constexpr int kThreads = W * 32;
     const int pieces_per_row = cols >> 3;
@@ -158,8 +160,7 @@ __device__ __forceinline__ void stage_x(uint4* xs, const StreamArgs& a, int k0, 
                 v = make_uint4(h[0] | h[1] << 16, h[2] | h[3] << 16, h[4] | h[5] << 16, h[6] | h[7] << 16);
             }
         }
-        const int key = ((m & 1) << 2) | (T & 3);
-        xs[(T * MP + m) * 8 + (c ^ key)] = v;
+        *reinterpret_cast<uint4*>(xs + T * stream_x_chunk_bytes(MP) + m * 144 + c * 16) = v;
     }
 }
 
@@ -177,8 +178,8 @@ w4a16_stream_kernel(const StreamArgs a) {
     constexpr int MP = MT * 8;
     constexpr int kWarps = W;
     constexpr int kBarBytes = stream_bar_bytes(W), kRingBytes = stream_ring_bytes(W);
-    constexpr int kPhaseCols = stream_x_bytes(W) / (MP * 2);   // W=16: 4096, 2048, 1024, 512 columns
-    constexpr int kPhaseBlocks = kPhaseCols / kBlockCols;
+    constexpr int kChunk = stream_x_chunk_bytes(MP);
+    constexpr int kPhaseBlocks = stream_x_bytes(W) / (4 * kChunk);   // W=16: 16, 8, 4, 2 column blocks
     static_assert(kPhaseBlocks >= 1, "x phase must hold at least one column block");
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -195,7 +196,7 @@ w4a16_stream_kernel(const StreamArgs a) {
     const uint32_t bar0 = smem_u32(smem) + warp * kStages * 8;
     uint8_t* ring = smem + kBarBytes + warp * kStages * kBlockBytes;
     const uint32_t ring0 = smem_u32(ring);
-    uint4* xs = reinterpret_cast<uint4*>(smem + kBarBytes + kRingBytes);
+    uint8_t* xs = smem + kBarBytes + kRingBytes;
 
     // Copy-request cursor (used by lane 0): image block (fkb, 16*fgrp + warp).  Consecutive
     // column blocks of one row tile are `stride` bytes apart; at the end of a row group the
@@ -226,7 +227,6 @@ w4a16_stream_kernel(const StreamArgs a) {
     }
     __syncwarp();
 
-    const int xkey = ((g & 1) << 2) | t;
     float acc[MT][4];
     int stage = 0;
     uint32_t parity = 0;
@@ -273,14 +273,15 @@ w4a16_stream_kernel(const StreamArgs a) {
                 const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);   // even nibbles: (1024+q) - (1024+z)
                 const float eg = -(64.0f + zg), eh = -(64.0f + zh);       // odd nibbles: (1024+16q)/16 - (64+z)
                 const float sg = step.x, sh = step.y;
-                const uint4* xchunk = xs + ((kb - p0) * 4 + t) * (MP * 8) + g * 8;
+                const uint8_t* xchunk = xs + ((kb - p0) * 4 + t) * kChunk + g * 144;
 #pragma unroll
                 for (int wi = 0; wi < 8; ++wi) {
                     const uint32_t wa = pick(code[wi >> 2], wi & 3);        // row g
                     const uint32_t wb = pick(code[2 + (wi >> 2)], wi & 3);  // row g+8
                     uint4 xv[MT];
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) xv[mt] = xchunk[mt * 64 + (wi ^ xkey)];
+                    for (int mt = 0; mt < MT; ++mt)
+                        xv[mt] = *reinterpret_cast<const uint4*>(xchunk + mt * (8 * 144) + wi * 16);
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
