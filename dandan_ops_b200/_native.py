@@ -33,6 +33,7 @@ _SIGNATURES = {
     "b2_w4a16_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "b2_w4a16_status": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_uint)]),
     "b2_w4a16_linear": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_linear_static": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "b2_w4a16_linear_route": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_plan": (_int, [_i64, _i64, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int),
                              ctypes.POINTER(_int), ctypes.POINTER(_int)]),
@@ -164,6 +165,21 @@ def status(device=None):
         word = ctypes.c_uint(0)
         _check(lib.b2_w4a16_status(ws.data_ptr(), _stream(), ctypes.byref(word)))
     return int(word.value)
+
+
+STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
+
+
+def linear_static(x, image, n, k, out):
+    """`b2_w4a16_linear_static`: at most 64 rows of x, scratch built into the library, nothing
+    allocated - the caller provides `out` ([M, N] FP16).  See include/b2_w4a16.h for the rules
+    (first call on a device before any stream capture; overlapping calls race)."""
+    lib = load()
+    m = x.shape[0]
+    with torch.cuda.device(x.device):
+        _check(lib.b2_w4a16_linear_static(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
+                                          out.data_ptr(), out.stride(0), m, n, k, _stream()))
+    return out
 
 
 def linear(x, image, n, k, route=ROUTE_AUTO, out=None):

@@ -166,6 +166,32 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
     return B2_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Built-in scratch for b2_w4a16_linear_static: a fixed array in device memory that every GPU
+// loading this library carries until the process exits.  In host code the symbol below is
+// only a handle; the kernels get the address that cudaGetSymbolAddress reports for the
+// current device.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[B2_W4A16_STATIC_SCRATCH_BYTES];
+
+int static_scratch(void** out) {
+    static void* address[64];
+    static std::atomic<bool> ready[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail("cudaGetDevice", e);
+    if (dev < 0 || dev >= 64) return fail(B2_ERR_UNSUPPORTED, "device ordinal out of range");
+    if (!ready[dev].load(std::memory_order_acquire)) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);      // address on the current device
+        if (e != cudaSuccess) return cuda_fail("cudaGetSymbolAddress", e);
+        address[dev] = ptr;
+        ready[dev].store(true, std::memory_order_release);
+    }
+    *out = address[dev];
+    return B2_OK;
+}
+
 int64_t stream_workspace_bytes(int64_t m, const b2::Dims& d, int sm_count) {
     // The first launch has the most rows; later chunks never need more.
     const StreamPlan p = plan_stream(m, d, sm_count);
@@ -381,6 +407,30 @@ int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* 
         return run_gemm(x, ldx, native, y, ldy, m, d, workspace, static_cast<cudaStream_t>(stream));
     }
     return fail(B2_ERR_UNSUPPORTED, "unknown route");
+}
+
+int b2_w4a16_linear_static(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
+                           int64_t m, int64_t n, int64_t k, void* stream) {
+    if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
+    if (int rc = check_dims(n, k)) return rc;
+    if (m > B2_STREAM_MAX_M)
+        return fail(B2_ERR_RANGE, "b2_w4a16_linear_static takes at most 64 rows of x per call");
+    if (m == 0) return B2_OK;
+    DeviceInfo dev;
+    if (int rc = device_info(dev)) return rc;
+    const b2::Dims d = b2::make_dims(n, k);
+    const int64_t need = stream_workspace_bytes(m, d, dev.sm_count);
+    if (need > B2_W4A16_STATIC_SCRATCH_BYTES)
+        return fail(B2_ERR_RANGE, "this problem needs " + std::to_string(need) +
+                    " bytes of scratch; the built-in scratch of b2_w4a16_linear_static holds " +
+                    std::to_string(B2_W4A16_STATIC_SCRATCH_BYTES) + " (use b2_w4a16_linear with a workspace)");
+    void* scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+    // The array keeps whatever the previous call left; the tickets must start at zero.
+    const cudaError_t e = cudaMemsetAsync(scratch, 0, B2_W4A16_TICKET_BYTES, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail("cudaMemsetAsync", e);
+    return b2_w4a16_linear_route(x, ldx, native, y, ldy, m, n, k, scratch, B2_W4A16_STATIC_SCRATCH_BYTES, stream,
+                                 B2_ROUTE_STREAM);
 }
 
 int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,

@@ -114,6 +114,31 @@ int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int
                     int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes,
                     void* stream);
 
+/* No counterpart in the reference.  y = x @ W^T for at most B2_STREAM_MAX_M rows of x, with
+ * the scratch memory built into the library instead of a caller-supplied workspace.
+ *
+ * For callers that cannot hand over device memory of their own and must not allocate:
+ * an operator slot whose interface passes only inputs and outputs (no workspace
+ * argument), a runtime whose memory is planned ahead and frozen, code running where
+ * cudaMalloc would stall the device or is simply forbidden.  This call allocates
+ * nothing - no cudaMalloc/cudaFree, no allocating library routine - and needs nothing
+ * from the caller beyond x, the weight image and y.
+ *
+ * The scratch is one fixed array of B2_W4A16_STATIC_SCRATCH_BYTES in device memory; every
+ * GPU that loads this library holds it until the process exits.  Limits and rules:
+ *   - m <= B2_STREAM_MAX_M and b2_w4a16_workspace_bytes(m,n,k) <= B2_W4A16_STATIC_SCRATCH_BYTES,
+ *     otherwise B2_ERR_RANGE with a message naming both sizes (always uses the streaming
+ *     kernel);
+ *   - the first call on a device looks up the array's device address (one runtime query, no
+ *     allocation); make that first call before starting any stream capture;
+ *   - all calls on a device share the array and it keeps the previous call's contents; each
+ *     call re-zeroes the part that must start at zero (an async memset on `stream`);
+ *   - two calls that overlap on the GPU (different streams, or graphs replayed concurrently)
+ *     race on the array: serialize them, or give one of them b2_w4a16_linear and a workspace. */
+#define B2_W4A16_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int b2_w4a16_linear_static(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
+                           int64_t m, int64_t n, int64_t k, void* stream);
+
 /* Same with an explicit kernel family (B2_ROUTE_*), for tests and benchmarks. */
 int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
                           int64_t m, int64_t n, int64_t k, void* workspace,
