@@ -284,7 +284,7 @@ def run_gpu(args, rank, world, local_rank):
                        "gather": bool(gather_layers)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "w4a16_stream_kernel",
+                         "kernel": "w4a16_tile_kernel" if args.workload == "qwen3-0.6b-decode" else "w4a16_stream_kernel",
                          "note": "achieved = algorithmic bytes per launch / average launch time over the graph"},
             "cpu_baseline": cpu,
             "e2e": {"value": round(weight_total / (e2e_ms_per_step * 1e-3) / 1e9, 2), "unit": "GB/s",

@@ -11,8 +11,8 @@ import torch
 from . import build as _build
 
 OK = 0
-ROUTE_AUTO, ROUTE_STREAM, ROUTE_TCGEN05 = 0, 1, 2
-ROUTE_NAMES = {ROUTE_STREAM: "b200_stream", ROUTE_TCGEN05: "b200_tcgen05"}
+ROUTE_AUTO, ROUTE_STREAM, ROUTE_TCGEN05, ROUTE_TILE = 0, 1, 2, 3
+ROUTE_NAMES = {ROUTE_STREAM: "b200_stream", ROUTE_TCGEN05: "b200_tcgen05", ROUTE_TILE: "b200_tile"}
 STREAM_MAX_M = 64
 TICKET_BYTES = 16384
 

@@ -12,6 +12,7 @@
 #include "layout_kernels.cuh"
 #include "stream_kernel.cuh"
 #include "gemm_kernel.cuh"
+#include "tile_kernel.cuh"
 
 namespace {
 
@@ -93,7 +94,7 @@ StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     if (p.mt == 8) p.warps = 16;                      // the 16 KB x buffer of a 4-warp CTA cannot hold 64 rows
     p.groups = (d.n16 + p.warps - 1) / p.warps;
     p.steps = (long long)p.groups * d.kb;
-    const long long slots = (long long)sms * (p.warps == 16 ? 1 : 4);
+    const long long slots = (long long)sms * (p.warps == 16 ? B2_STREAM_CTAS16 : 4);
     p.grid = int(p.steps < slots ? p.steps : slots);
     const long long per_cta = p.steps / p.grid;       // >= 1
     long long parts = (d.kb + per_cta - 1) / per_cta + 1;
@@ -131,6 +132,51 @@ int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaS
             return xvec ? launch_stream_one<MT, true, 16>(a, grid, s) : launch_stream_one<MT, false, 16>(a, grid, s);
         return xvec ? launch_stream_one<MT, true, 4>(a, grid, s) : launch_stream_one<MT, false, 4>(a, grid, s);
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Latency-oriented tile kernel: whole K of one row tile per CTA (small and mid-size layers).
+// ---------------------------------------------------------------------------------------
+constexpr int kTileSmemLimit = 200 * 1024;
+constexpr int64_t kTileMaxBlocks = 4096;       // native blocks (9.6 MB of image); larger layers stream
+
+bool tile_applicable(int64_t rows, const b2::Dims& d) {
+    if (rows > 16) return false;
+    const int mt = rows <= 8 ? 1 : 2;
+    const int warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
+    return int64_t(d.n16) * d.kb <= kTileMaxBlocks && b2::tile_smem_bytes(d.kb, mt, warps) <= kTileSmemLimit;
+}
+
+template <int MT, bool XVEC>
+int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
+    auto kernel = b2::w4a16_tile_kernel<MT, XVEC>;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemLimit);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<a.n16, a.warps * 32, smem, s>>>(a);
+    return after_launch("w4a16_tile_kernel");
+}
+
+int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s) {
+    b2::TileArgs a;
+    a.x = static_cast<const __half*>(x);
+    a.native = static_cast<const uint8_t*>(native);
+    a.y = static_cast<__half*>(y);
+    a.status = workspace ? static_cast<unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1) : nullptr;
+    a.ldx = ldx; a.ldy = ldy;
+    a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
+    a.warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
+    const int mt = rows <= 8 ? 1 : 2;
+    const int smem = b2::tile_smem_bytes(d.kb, mt, a.warps);
+    if (mt == 1) return xvec ? launch_tile_one<1, true>(a, smem, s) : launch_tile_one<1, false>(a, smem, s);
+    return xvec ? launch_tile_one<2, true>(a, smem, s) : launch_tile_one<2, false>(a, smem, s);
 }
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
@@ -351,6 +397,13 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
         if (rows_per_launch) *rows_per_launch = int(m);
         return B2_OK;
     }
+    if (m > 0 && tile_applicable(m, d)) {          // whole K of a row tile per CTA, no split between CTAs
+        if (route) *route = B2_ROUTE_TILE;
+        if (k_splits) *k_splits = 1;
+        if (grid) *grid = d.n16;
+        if (rows_per_launch) *rows_per_launch = int(m);
+        return B2_OK;
+    }
     if (route) *route = B2_ROUTE_STREAM;
     if (k_splits) *k_splits = p.max_parts;
     if (grid) *grid = p.grid;
@@ -395,7 +448,14 @@ int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* 
     if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     const b2::Dims d = b2::make_dims(n, k);
     if (route == B2_ROUTE_AUTO)
-        route = (m > B2_STREAM_MAX_M && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
+        route = tile_applicable(m, d) ? B2_ROUTE_TILE
+              : (m > B2_STREAM_MAX_M && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
+    if (route == B2_ROUTE_TILE) {
+        if (!tile_applicable(m, d))
+            return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
+        const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream));
+    }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
                           static_cast<cudaStream_t>(stream), dev);

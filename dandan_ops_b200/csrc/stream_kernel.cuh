@@ -42,12 +42,18 @@
 
 namespace b2 {
 
-constexpr int kStages = 4;                   // ring depth per warp
+#ifndef B2_STREAM_STAGES
+#define B2_STREAM_STAGES 4
+#endif
+#ifndef B2_STREAM_CTAS16
+#define B2_STREAM_CTAS16 1
+#endif
+constexpr int kStages = B2_STREAM_STAGES;    // ring depth per warp
 // Shared-memory budget of a CTA with W warps (W = 16: one CTA per SM; W = 4: four per SM,
 // for layers with too few steps to feed 16-warp CTAs on every SM).
 __host__ __device__ constexpr int stream_bar_bytes(int w) { return w * kStages * 8; }
 __host__ __device__ constexpr int stream_ring_bytes(int w) { return w * kStages * kBlockBytes; }
-__host__ __device__ constexpr int stream_x_bytes(int w) { return w * 4736; }   // 74 KB / 18.5 KB
+__host__ __device__ constexpr int stream_x_bytes(int w) { return w == 16 ? w * 4736 / B2_STREAM_CTAS16 : w * 4736; }   // 74 KB / 18.5 KB
 // Staged x: 64-column chunk T, row m, 16-byte piece c at T*chunk + m*144 + c*16.  Rows are padded
 // to 144 bytes and chunks by 32 more, which spreads the eight lanes of a quarter warp (two rows x
 // four chunks) over all eight 16-byte bank groups without any address arithmetic per piece.
@@ -172,7 +178,7 @@ __device__ __forceinline__ int owner_of(long long s, long long steps, int ctas) 
 // MT = number of 8-row tiles of x (1, 2, 4 or 8).  XVEC: x rows are 16-byte aligned and
 // K is a multiple of 8, so x is read with 16-byte loads.
 template <int MT, bool XVEC, int W>
-__global__ void __launch_bounds__(W * 32, (W == 16 ? 1 : 4))
+__global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
 w4a16_stream_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MP = MT * 8;

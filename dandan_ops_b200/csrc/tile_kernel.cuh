@@ -1,0 +1,157 @@
+// Latency-oriented kernel for small and mid-size layers in the decode regime (M <= 16).
+//
+// On layers of a few megabytes the streaming kernel is bound by latency, not bandwidth: a
+// warp needs ~0.5 us to decode one native block, and splitting K between CTAs costs a trip
+// through global memory.  This kernel puts the whole K range of one row tile (16 outputs)
+// into one CTA and brings every one of its native blocks in flight at once:
+//   * one bulk copy and one mbarrier per native block, all issued by the first thread before
+//     anything else happens (kb * 2336 bytes in flight per CTA, several CTAs per SM);
+//   * the unit of work is half a block (eight of its sixteen MMA steps); up to 16 warps take
+//     consecutive units, so a block is decoded by two warps in parallel;
+//   * x for the whole K range is staged once per CTA in the padded conflict-free layout of
+//     the streaming kernel;
+//   * the per-warp FP32 accumulator tiles are added in warp order through shared memory, so
+//     the result is bit-reproducible and no workspace, ticket or partial tile is needed.
+// The dequantization chain and the MMA fragment layout are those of stream_kernel.cuh.
+#pragma once
+#include "layout.cuh"
+#include "stream_kernel.cuh"
+
+namespace b2 {
+
+constexpr int kTileMaxWarps = 16;
+
+struct TileArgs {
+    const __half* x;
+    const uint8_t* native;
+    __half* y;
+    unsigned* status;       // may be null
+    int64_t ldx, ldy;
+    int m, n, k;
+    int n16, kb;
+    int warps;              // warps per CTA = min(16, 2*kb)
+};
+
+__host__ __device__ constexpr int tile_smem_bytes(int kb, int mt, int warps) {
+    // barriers (padded to 128) + blocks + staged x + reduction tiles
+    return ((kb * 8 + 127) / 128) * 128 + kb * kBlockBytes + kb * 4 * stream_x_chunk_bytes(mt * 8) +
+           warps * mt * 512;
+}
+
+template <int MT, bool XVEC>
+__global__ void __launch_bounds__(kTileMaxWarps * 32)
+w4a16_tile_kernel(const TileArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int MP = MT * 8;
+    constexpr int kChunk = stream_x_chunk_bytes(MP);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int nt = blockIdx.x;
+    const int bar_bytes = ((a.kb * 8 + 127) / 128) * 128;
+    uint8_t* blocks = smem + bar_bytes;
+    uint8_t* xs = blocks + a.kb * kBlockBytes;
+    float4* red = reinterpret_cast<float4*>(xs + a.kb * 4 * kChunk);
+    const uint32_t bar0 = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < a.kb; ++b) mbar_init(bar0 + b * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const uint8_t* src = a.native + int64_t(nt) * kBlockBytes;
+        const int64_t stride = int64_t(a.n16) * kBlockBytes;
+        for (int b = 0; b < a.kb; ++b) {
+            mbar_expect_tx(bar0 + b * 8, kBlockBytes);
+            bulk_copy_g2s(smem_u32(blocks + b * kBlockBytes), src + b * stride, kBlockBytes, bar0 + b * 8);
+        }
+    }
+    // stage x for all columns (zero beyond M and K)
+    {
+        const int pieces_per_row = a.kb * 32;
+        const int total = MP * pieces_per_row;
+        for (int i = threadIdx.x; i < total; i += blockDim.x) {
+            const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
+            const int k = cc * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (m < a.m && k < a.k) {
+                const __half* src = a.x + int64_t(m) * a.ldx + k;
+                if constexpr (XVEC) {
+                    v = __ldg(reinterpret_cast<const uint4*>(src));
+                } else {
+                    uint32_t h[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        h[e] = (k + e < a.k) ? uint32_t(__half_as_ushort(__ldg(src + e))) : 0u;
+                    v = make_uint4(h[0] | h[1] << 16, h[2] | h[3] << 16, h[4] | h[5] << 16, h[6] | h[7] << 16);
+                }
+            }
+            *reinterpret_cast<uint4*>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16) = v;
+        }
+    }
+    __syncthreads();        // x staged; barrier initialisation visible to every waiter
+
+    // units = half blocks, dealt in consecutive runs to the warps
+    const int units = a.kb * 2;
+    const int u0 = (units * warp) / a.warps, u1 = (units * (warp + 1)) / a.warps;
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
+    bool failed = false;
+    for (int u = u0; u < u1 && !failed; ++u) {
+        const int b = u >> 1, h = u & 1;
+        if (!mbar_wait(bar0 + b * 8, 0)) {
+            failed = true;
+            if (lane == 0 && a.status) atomicOr(a.status, kStatusCopyTimeout);
+            break;
+        }
+        const uint8_t* slot = blocks + b * kBlockBytes;
+        const uint4 ca = *reinterpret_cast<const uint4*>(slot + h * 512 + lane * 16);         // row g
+        const uint4 cb = *reinterpret_cast<const uint4*>(slot + (2 + h) * 512 + lane * 16);   // row g+8
+        const float2 step = *reinterpret_cast<const float2*>(slot + kStepOffset + lane * 8);
+        const uint32_t zero = slot[kZeroOffset + lane];
+        const float zg = float(zero & 15u), zh = float(zero >> 4);
+        const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);
+        const float eg = -(64.0f + zg), eh = -(64.0f + zh);
+        const float sg = step.x, sh = step.y;
+        const uint8_t* xchunk = xs + (b * 4 + t) * kChunk + g * 144 + h * 64;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t wa = pick(ca, i), wb = pick(cb, i);
+            uint4 xv[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                xv[mt] = *reinterpret_cast<const uint4*>(xchunk + mt * (8 * 144) + i * 16);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
+                float d[8];
+                add_mixed(and_or(ua, 0x000F000Fu, 0x64006400u), cg, d[0], d[1]);
+                add_mixed(and_or(ub, 0x000F000Fu, 0x64006400u), ch, d[2], d[3]);
+                fma_mixed_16th(and_or(ua, 0x00F000F0u, 0x64006400u), eg, d[4], d[5]);
+                fma_mixed_16th(and_or(ub, 0x00F000F0u, 0x64006400u), eh, d[6], d[7]);
+                const uint32_t w[4] = {scale_pack(d[0], d[1], sg), scale_pack(d[2], d[3], sh),
+                                       scale_pack(d[4], d[5], sg), scale_pack(d[6], d[7], sh)};
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                    mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
+            }
+        }
+    }
+    // Blocks this CTA requested but no warp waited for cannot exist: every block has two units.
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+        red[(warp * MT + mt) * 32 + lane] = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
+    __syncthreads();
+    // thread e adds element e of every warp's tile in warp order and stores one output
+    for (int e = threadIdx.x; e < MT * 128; e += blockDim.x) {
+        const int mt = e >> 7, rl = (e >> 2) & 31, c = e & 3;
+        float sum = 0.0f;
+        for (int w = 0; w < a.warps; ++w)
+            sum += reinterpret_cast<const float*>(red)[((w * MT + mt) * 32 + rl) * 4 + c];
+        const int rg = rl >> 2, rt = rl & 3;
+        const int m = mt * 8 + 2 * rt + (c & 1), n = nt * 16 + rg + 8 * (c >> 1);
+        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = __float2half_rn(sum);
+    }
+}
+
+}  // namespace b2

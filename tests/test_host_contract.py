@@ -37,7 +37,9 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     assert _native.native_bytes(2048, 1024) == 128 * 4 * 2336
     assert _native.native_bytes(16, 256) == 2336 and _native.native_bytes(17, 257) == 4 * 2336
     plan = _native.plan(8, 2048, 1024)
-    assert plan["route"] == "b200_stream" and plan["grid"] >= 1
+    assert plan["route"] == "b200_tile" and plan["grid"] == 128
+    assert _native.plan(8, 57344, 8192)["route"] == "b200_stream"
+    assert _native.plan(32, 2048, 1024)["route"] == "b200_stream"
     assert _native.plan(512, 4096, 4096)["route"] == "b200_tcgen05"
     assert _native.plan(512, 4096, 4097)["route"] == "b200_stream"       # K % 8 != 0
     lib2 = _native.load()

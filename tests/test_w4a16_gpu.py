@@ -91,7 +91,7 @@ def test_cpu_runnable_config():
     y = layer(x.cuda())
     assert_close_ref(y, ARR["cfg1_y"])
     info = layer.execution_info(x.cuda())
-    assert set(c["info"]) <= set(info) and info["implementation"] == "b200_stream"
+    assert set(c["info"]) <= set(info) and info["implementation"] == "b200_tile"
     assert info["format_version"] == 2 and info["input_copies"] == []
     # run-to-run determinism of the split-K reduction
     assert torch.equal(y, layer(x.cuda()))
@@ -322,3 +322,42 @@ def test_tcgen05_unaligned_falls_back_and_graph_replay():
     graph.replay()
     torch.cuda.synchronize()
     assert torch.count_nonzero(out) == 0
+
+
+# ------------------------------------------------------------------------------------------
+# the three decode/prefill kernel families agree with each other and with the oracle
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(1, 1000, 1024), (3, 37, 257), (8, 2048, 1024), (16, 1024, 3072), (5, 12289, 1024),
+                                   (16, 4096, 4096), (1, 16, 6912), (9, 100, 264)])
+def test_tile_and_stream_routes_agree(m, n, k):
+    g = torch.Generator().manual_seed(m * 7 + n + k)
+    layer = ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.03).half().cuda())
+    x = torch.randn(m, k, generator=g).half().cuda()
+    image = layer._native_image()
+    tile = _native.linear(x, image, n, k, route=_native.ROUTE_TILE)
+    stream = _native.linear(x, image, n, k, route=_native.ROUTE_STREAM)
+    assert _native.status() == 0
+    want = oracle_y(x, layer)
+    assert_close_ref(tile, want)
+    assert_close_ref(stream, want)
+    assert torch.equal(tile, _native.linear(x, image, n, k, route=_native.ROUTE_TILE))     # reproducible
+    assert torch.equal(stream, _native.linear(x, image, n, k, route=_native.ROUTE_STREAM))
+    assert torch.equal(layer(x), tile)                                                   # what AUTO picks here
+    eye = torch.eye(k, dtype=torch.float16, device="cuda")[:min(k, 8)]
+    w = oracle.dequantize_fp16(layer.packed_weight.cpu().numpy(), layer.scales.cpu().numpy(),
+                               layer.zeros.cpu().numpy(), k)
+    got = _native.linear(eye, image, n, k, route=_native.ROUTE_TILE).t().contiguous().cpu().numpy()
+    assert np.array_equal(got, w[:, :eye.shape[0]])
+
+
+def test_route_limits_are_reported():
+    layer = ops.QuantizedLinear.from_float(torch.randn(64, 512, dtype=torch.float16).cuda())
+    image = layer._native_image()
+    with pytest.raises(RuntimeError, match="tile route"):
+        _native.linear(torch.zeros(17, 512, dtype=torch.float16, device="cuda"), image, 64, 512, route=_native.ROUTE_TILE)
+    big = ops.QuantizedLinear.from_float(torch.randn(16, 28672, dtype=torch.float16).cuda())
+    with pytest.raises(RuntimeError, match="tile route"):
+        _native.linear(torch.zeros(1, 28672, dtype=torch.float16, device="cuda"), big._native_image(), 16, 28672,
+                       route=_native.ROUTE_TILE)
+    with pytest.raises(RuntimeError, match="route"):
+        _native.linear(torch.zeros(1, 512, dtype=torch.float16, device="cuda"), image, 64, 512, route=9)

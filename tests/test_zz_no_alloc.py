@@ -39,8 +39,10 @@ def test_static_scratch_entry_matches_workspace_entry_twice(m, n, k):
     for x, y in zip((x1, x2), outs):
         want = _native.linear(x, image, n, k)              # existing entry point, caller-owned workspace
         torch.testing.assert_close(y, want, atol=ATOL, rtol=RTOL)
-        assert torch.equal(y, want)                        # same kernel, same plan: identical bits
-    assert torch.equal(_native.linear_static(x1, image, n, k, outs[0]), _native.linear(x1, image, n, k))
+        same_kernel = _native.linear(x, image, n, k, route=_native.ROUTE_STREAM)
+        assert torch.equal(y, same_kernel)                 # same kernel, same plan: identical bits
+    assert torch.equal(_native.linear_static(x1, image, n, k, outs[0]),
+                       _native.linear(x1, image, n, k, route=_native.ROUTE_STREAM))
 
 
 def test_static_scratch_entry_rejects_what_it_cannot_hold():
