@@ -48,12 +48,15 @@ import torch
 WORKLOADS = {
     "qwen3-0.6b-decode": {"shapes": [("qkv", 4096, 1024), ("o", 1024, 2048), ("gate_up", 6144, 1024),
                                      ("down", 1024, 3072)],
-                          "layers": 28, "ms": [1, 2, 4, 8], "sigma": 0.02, "seed": 1000, "shard": False},
+                          "layers": 28, "ms": [1, 2, 4, 8], "detail_ms": [16, 512], "sigma": 0.02, "seed": 1000,
+                          "shard": False},
     "qwen3-8b-layer": {"shapes": [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096),
                                   ("down", 4096, 12288)],
-                       "layers": 3, "ms": [1, 16], "sigma": 0.02, "seed": 2000, "shard": False},
+                       "layers": 3, "ms": [1, 16], "detail_ms": [8, 512, 2048], "sigma": 0.02, "seed": 2000,
+                       "shard": False},
     "llama3-70b-mlp": {"shapes": [("gate_up", 57344, 8192), ("down", 8192, 28672)],
-                       "layers": 1, "ms": [1, 8], "sigma": 0.015, "seed": 3000, "shard": True},
+                       "layers": 1, "ms": [1, 8], "detail_ms": [16, 256, 4096], "sigma": 0.015, "seed": 3000,
+                       "shard": True},
 }
 FALLBACK_HBM_GBS = 6650.0
 
@@ -261,7 +264,20 @@ def run_gpu(args, rank, world, local_rank):
     ms_per_step, e2e_ms_per_step = (float(v) for v in times.cpu())
     weight_total, alg_total = (float(v) for v in bytes_all.cpu())
 
-    detail = per_shape_detail(spec, layers, x_dev, stream) if (rank == 0 and not args.no_detail) else None
+    detail = None
+    if rank == 0 and not args.no_detail:
+        detail = {args.workload: per_shape_detail(spec, layers, x_dev, stream, device)}
+        if world == 1 and not args.workload_only:
+            # the other BASELINE configurations, one table each (decode GB/s and prefill TFLOP/s)
+            for other in sorted(WORKLOADS):
+                if other == args.workload:
+                    continue
+                ospec = dict(WORKLOADS[other])
+                ospec["layers"] = min(ospec["layers"], 2)
+                olayers = build_layers(ospec, 0, 1, device)
+                detail[other] = per_shape_detail(ospec, olayers, make_inputs(ospec, device), stream, device)
+                del olayers
+                torch.cuda.empty_cache()
     cpu = cpu_baseline(spec, sample_seconds=args.cpu_seconds) if (rank == 0 and world == 1 and not args.no_cpu) else None
 
     if rank == 0:
@@ -301,10 +317,13 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def per_shape_detail(spec, layers, x_dev, stream):
+def per_shape_detail(spec, layers, x_dev, stream, device):
     """Median CUDA-graph replay time of every (projection, M): microseconds, weight GB/s, TFLOPS.
-    Each graph walks all layers of the workload, so consecutive launches never reuse weights."""
+    Each graph walks all layers of the workload, so consecutive launches never reuse weights
+    (single layers larger than L2 need no rotation).  `detail_ms` adds batch sizes that are not
+    part of the timed step, among them the prefill sizes that run on the tcgen05 GEMM."""
     out = []
+    gen = torch.Generator().manual_seed(spec["seed"] + 6)
     with torch.cuda.stream(stream):
         for si, (name, n_full, k) in enumerate(spec["shapes"]):
             column = [row[si] for row in layers if row[si][3] is not None]
@@ -312,8 +331,12 @@ def per_shape_detail(spec, layers, x_dev, stream):
                 continue
             n = column[0][1]
             reps = max(1, int(300e6 // max(1.0, len(column) * weight_bytes(n, k))))
-            for m in spec["ms"]:
-                x = x_dev[(m, k)]
+            for m in sorted(set(spec["ms"]) | set(spec.get("detail_ms", []))):
+                x = x_dev.get((m, k))
+                if x is None:
+                    x = torch.randn(m, k, generator=gen).half().to(device)
+                if m > 64:
+                    reps = 1
                 for _, _, _, layer in column:
                     layer(x)
                 stream.synchronize()
@@ -332,6 +355,7 @@ def per_shape_detail(spec, layers, x_dev, stream):
                     samples.append(e0.elapsed_time(e1) * 1e3 / (reps * len(column)))
                 us = statistics.median(samples)
                 out.append({"proj": name, "N": n, "K": k, "M": m, "us": round(us, 2),
+                            "kernel": layer.execution_info(x)["implementation"],
                             "weight_GBps": round(weight_bytes(n, k) / us / 1e3, 1),
                             "TFLOPS": round(2.0 * m * n * k / us / 1e6, 2)})
     return out
@@ -428,6 +452,7 @@ def main():
     ap.add_argument("--gather", action="store_true", help="all-gather output slices (sharded workload, N>1)")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload-only", action="store_true", help="per-shape table for the chosen workload only")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

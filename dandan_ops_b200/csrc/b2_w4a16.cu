@@ -161,6 +161,7 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
     }
     kernel<<<a.n16, a.warps * 32, smem, s>>>(a);
     return after_launch("w4a16_tile_kernel");
+
 }
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
