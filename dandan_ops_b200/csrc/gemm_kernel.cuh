@@ -1,18 +1,18 @@
 // Prefill kernel: y[M,N] = x[M,K] @ W^T on the 5th-generation tensor cores (tcgen05).
 //
-// One CTA computes a tile of up to 256 rows of x by 128 output columns:
-//   D[m][n] (FP32, tensor memory, 128 lanes x 128 columns per accumulator, MA accumulators)
+// One CTA computes a tile of 128 rows of x by 128 output columns, or 256 rows by 192 columns:
+//   D[m][n] (FP32, tensor memory, 128 lanes x BN columns per accumulator, MA accumulators)
 //     += A[m][k] (x tile, FP16, shared memory, loaded by TMA with the 128-byte swizzle)
 //      * B[n][k] (weight tile, FP16, shared memory, written by the converter warps)
 // in steps of 64 columns of K (one quantization group per weight row).
 //
-// Warp roles (10 warps, 320 threads):
-//   warp 0      copy producer: per 256-column block one bulk copy of the 8 native weight
-//               blocks of the tile (18.7 KB, contiguous in the image) into the raw ring, and
+// Warp roles (2 + BN/16 warps):
+//   warp 0      copy producer: per 256-column block one bulk copy of the BN/16 native weight
+//               blocks of the tile (contiguous in the image) into the raw ring, and
 //               per 64-column step the TMA loads of the x tile(s)
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane) and
 //               tcgen05.commit, frees tensor memory
-//   warps 2-9   converters: dequantize the 4-bit codes of one 64-column step exactly
+//   warps 2..   converters: dequantize the 4-bit codes of one 64-column step exactly
 //               (w = fp16_rn(fp32(code - zero) * step)) and store the FP16 tile in the
 //               canonical K-major 128-byte-swizzled layout the MMA descriptor expects;
 //               afterwards the same warps run the epilogue (tcgen05.ld -> FP16 -> global)
@@ -20,9 +20,9 @@
 // Rings and barriers (every wait is bounded; a wait that gives up raises the CTA's abort
 // flag, records kStatusGemmTimeout in the status word and all roles leave):
 //   raw_full[r]  tx-count barrier, completed by the bulk copy of raw stage r
-//   raw_free[r]  8 arrivals (one per converter warp) after the last read of raw stage r
+//   raw_free[r]  one arrival per converter warp after the last read of raw stage r
 //   a_full[s]    tx-count barrier, completed by the TMA load(s) of x for step-stage s
-//   b_full[s]    8 arrivals (one per converter warp, after fence.proxy.async)
+//   b_full[s]    one arrival per converter warp (after fence.proxy.async)
 //   ab_free[s]   tcgen05.commit after the MMAs that read stage s
 //   acc_full     tcgen05.commit after the last MMA of the tile
 //
@@ -37,20 +37,20 @@
 
 namespace b2 {
 
-constexpr int kGemmBN = 128;                    // output columns (weight rows) per CTA
+// BN = output columns (weight rows) per CTA: 192 when two accumulators are used (the x tiles
+// are re-read from L2 by every column tile, and L2 bandwidth is what bounds this kernel, so a
+// wider tile means proportionally less traffic per flop), 128 otherwise.
 constexpr int kGemmBK = 64;                     // K per step = one quantization group
-constexpr int kGemmRawStages = 3;               // ring of 256-column raw weight blocks
 constexpr int kGemmStages = 3;                  // ring of 64-column FP16 operand stages
-constexpr int kGemmRawBytes = (kGemmBN / 16) * kBlockBytes;        // 18688
-constexpr int kGemmBBytes = kGemmBN * kGemmBK * 2;                 // 16384
 constexpr int kGemmABytes = 128 * kGemmBK * 2;                     // 16384 per 128 rows of x
-constexpr int kGemmThreads = 320;
-constexpr int kGemmConverters = 8;              // converter warps
 constexpr unsigned kStatusGemmTimeout = 2u;
-
-__host__ __device__ constexpr int gemm_smem_bytes(int ma) {
+__host__ __device__ constexpr int gemm_raw_stages(int bn) { return bn == 128 ? 3 : 2; }   // 256-column raw blocks
+__host__ __device__ constexpr int gemm_raw_bytes(int bn) { return (bn / 16) * kBlockBytes; }
+__host__ __device__ constexpr int gemm_b_bytes(int bn) { return bn * kGemmBK * 2; }
+__host__ __device__ constexpr int gemm_threads(int bn) { return 64 + 2 * bn; }              // two roles + converters
+__host__ __device__ constexpr int gemm_smem_bytes(int ma, int bn) {
     // 1024-byte alignment slack + operand stages + raw ring + barriers/flags
-    return 1024 + kGemmStages * (kGemmBBytes + ma * kGemmABytes) + kGemmRawStages * kGemmRawBytes + 256;
+    return 1024 + kGemmStages * (gemm_b_bytes(bn) + ma * kGemmABytes) + gemm_raw_stages(bn) * gemm_raw_bytes(bn) + 256;
 }
 
 struct GemmArgs {
@@ -125,9 +125,11 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, float c_even, float c_
 
 // MA = accumulators of 128 rows of x each (1 or 2).  VEC: y rows may be written with
 // 16-byte stores (N % 8 == 0, ldy % 8 == 0, y 16-byte aligned).
-template <int MA, bool VEC>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int MA, int BN, bool VEC>
+__global__ void __launch_bounds__(gemm_threads(BN), 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
+    constexpr int kGemmBN = BN, kGemmRawStages = gemm_raw_stages(BN), kGemmRawBytes = gemm_raw_bytes(BN);
+    constexpr int kGemmBBytes = gemm_b_bytes(BN), kGemmConverters = BN / 16;   // converter warps
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -158,7 +160,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), MA * 128);
+    constexpr uint32_t kTmemCols = (MA * BN <= 128) ? 128 : (MA * BN <= 256) ? 256 : 512;
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -219,7 +222,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                     const uint32_t a_addr = b_addr + kGemmBBytes + i * kGemmABytes;
 #pragma unroll
                     for (int kk = 0; kk < kGemmBK / 16; ++kk)
-                        umma_f16(tmem_base + i * 128, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32),
+                        umma_f16(tmem_base + i * BN, umma_desc_sw128(a_addr + kk * 32), umma_desc_sw128(b_addr + kk * 32),
                                  idesc, (s > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(bar(AB_FREE + st));
@@ -229,7 +232,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         }
     } else {
         // ------------------------------ converters ---------------------------------------
-        const int ct = threadIdx.x - 64;              // 0..255
+        const int ct = threadIdx.x - 64;              // 0 .. 2*BN-1
         const int r = ct >> 1, h = ct & 1;            // weight row of the tile, half of the 64-column group
         const int blk = r >> 4, rr = r & 15, g = rr & 7, hi8 = rr >> 3;
         bool ok = true;
@@ -262,15 +265,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
         if (ok && wait(ACC_FULL, 0)) {
             tcgen05_fence_after();
             const int quad = warp & 3;                 // tensor-memory lanes 32*quad .. 32*quad+31
-            const int colhalf = (warp - 2) >> 2;       // warps 2-5 take columns 0-63, warps 6-9 columns 64-127
+            const int part = (warp - 2) >> 2;          // BN/64 warps share a lane quadrant, 64 columns each
 #pragma unroll
             for (int i = 0; i < MA; ++i) {
                 const int m = tile_m * (MA * 128) + i * 128 + quad * 32 + lane;
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
-                    const int col = colhalf * 64 + cc * 32;
+                    const int col = part * 64 + cc * 32;
                     uint32_t v[32];
-                    tmem_ld32(tmem_base + (uint32_t(quad * 32) << 16) + i * 128 + col, v);
+                    tmem_ld32(tmem_base + (uint32_t(quad * 32) << 16) + i * BN + col, v);
                     const int n0 = tile_n * kGemmBN + col;
                     if (m < a.m) {
                         __half* dst = a.y + int64_t(m) * a.ldy + n0;
@@ -299,7 +302,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
-        tmem_dealloc(tmem_base, MA * 128);
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
