@@ -238,6 +238,14 @@ w4a16_stream_kernel(const StreamArgs a) {
     uint32_t parity = 0;
     bool failed = false;
 
+    // When all of K fits in the x buffer it is staged once for the whole kernel: x does not
+    // depend on the row group, so the CTA never has to stop between row groups again.
+    const bool whole_x = a.kb <= kPhaseBlocks;
+    if (whole_x) {
+        stage_x<MT, XVEC, W>(xs, a, 0, a.kb * kBlockCols);
+        __syncthreads();
+    }
+
     long long s0 = b0;
     while (s0 < b1) {                                       // one iteration per row group in the range
         const int grp = int(s0 / a.kb);
@@ -252,9 +260,12 @@ w4a16_stream_kernel(const StreamArgs a) {
 
         for (int p0 = k_lo; p0 < k_hi; p0 += kPhaseBlocks) {
             const int p1 = min(k_hi, p0 + kPhaseBlocks);
-            __syncthreads();                               // everyone is done with the previous x phase
-            stage_x<MT, XVEC, W>(xs, a, p0 * kBlockCols, (p1 - p0) * kBlockCols);
-            __syncthreads();
+            if (!whole_x) {
+                __syncthreads();                           // everyone is done with the previous x phase
+                stage_x<MT, XVEC, W>(xs, a, p0 * kBlockCols, (p1 - p0) * kBlockCols);
+                __syncthreads();
+            }
+            const int xorigin = whole_x ? 0 : p0;          // column block that the x buffer starts at
             if (!active || failed) continue;
             for (int kb = p0; kb < p1; ++kb) {
                 if (!mbar_wait(bar0 + stage * 8, parity)) {
@@ -279,7 +290,7 @@ w4a16_stream_kernel(const StreamArgs a) {
                 const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);   // even nibbles: (1024+q) - (1024+z)
                 const float eg = -(64.0f + zg), eh = -(64.0f + zh);       // odd nibbles: (1024+16q)/16 - (64+z)
                 const float sg = step.x, sh = step.y;
-                const uint8_t* xchunk = xs + ((kb - p0) * 4 + t) * kChunk + g * 144;
+                const uint8_t* xchunk = xs + ((kb - xorigin) * 4 + t) * kChunk + g * 144;
 #pragma unroll
                 for (int wi = 0; wi < 8; ++wi) {
                     const uint32_t wa = pick(code[wi >> 2], wi & 3);        // row g
