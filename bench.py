@@ -209,7 +209,7 @@ def run_gpu(args, rank, world, local_rank):
             one_step()
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
-        use_graph = gather_layers is None
+        use_graph = gather_layers is None       # the NCCL gather is launched eagerly, not captured
         if use_graph:
             with torch.cuda.graph(graph, stream=stream):
                 one_step()
