@@ -182,16 +182,30 @@ def linear_static(x, image, n, k, out):
     return out
 
 
+_need_cache = {}
+
+
 def linear(x, image, n, k, route=ROUTE_AUTO, out=None):
     """y[M,N] = x[M,K] @ W^T on the current stream.  x must be CUDA FP16 with unit inner stride."""
-    lib = load()
+    lib = _lib if _lib is not None else load()
     m = x.shape[0]
-    with torch.cuda.device(x.device):
-        y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
-        if m == 0:
-            return y
-        need = lib.b2_w4a16_workspace_bytes(m, n, k)
-        ws = workspace(x.device, need)
-        _check(lib.b2_w4a16_linear_route(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(), y.data_ptr(),
-                                         y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), _stream(), route))
+    device = x.device
+    if torch.cuda.current_device() != device.index:      # rare: keep the common path free of context switches
+        with torch.cuda.device(device):
+            return linear(x, image, n, k, route, out)
+    y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=device)
+    if m == 0:
+        return y
+    key = (m if m <= STREAM_MAX_M else STREAM_MAX_M + 1, n, k, device.index)
+    need = _need_cache.get(key)
+    if need is None:
+        need = _need_cache[key] = int(lib.b2_w4a16_workspace_bytes(m, n, k))
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = _workspaces.get((device.index, stream))
+    if ws is None or ws.numel() < need:
+        ws = workspace(device, need)
+    rc = lib.b2_w4a16_linear_route(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(), y.data_ptr(),
+                                   y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream, route)
+    if rc != OK:
+        _check(rc)
     return y
