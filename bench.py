@@ -290,8 +290,9 @@ def run_gpu(args, rank, world, local_rank):
             "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None,
-            "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
+            "dtype": "f16", "data": "synthetic",
             "config": {"workload": args.workload, "layers": spec["layers"], "batch_sizes": spec["ms"],
+                       "arithmetic": "u4 codes, exact f16 weights, f16 activations, f32 accumulate, f16 output",
                        "shapes_NxK": [f"{n}x{k}" for _, n, k in spec["shapes"]],
                        "linears_per_step": len(calls), "weight_bytes_per_step_per_gpu": int(step_weight_bytes),
                        "native_image_bytes_resident_per_gpu": int(native_resident),
@@ -299,7 +300,11 @@ def run_gpu(args, rank, world, local_rank):
                        "timing": "step replayed as one CUDA graph" if use_graph else "eager launches",
                        "gather": bool(gather_layers)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "frac": round(achieved / peak, 4),
+                         # ncu (profiles/): DRAM bytes read+written = 1.015 x (tile kernel) / 1.005 x (streaming
+                         # kernel) the algorithmic weight bytes of a launch; scaled here to the average launch
+                         "traffic": round((step_weight_bytes / launches) * (1.015 if args.workload == "qwen3-0.6b-decode" else 1.005)),
+                         "traffic_unit": "bytes per launch", "peak_kind": peak_kind,
                          "kernel": "w4a16_tile_kernel" if args.workload == "qwen3-0.6b-decode" else "w4a16_stream_kernel",
                          "note": "achieved = algorithmic bytes per launch / average launch time over the graph"},
             "cpu_baseline": cpu,
@@ -434,7 +439,7 @@ def run_reference(args, rank, world):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(elapsed / args.steps * 1e3, 3), "higher_is_better": True,
         "scaling": "strong" if spec["shard"] else "weak", "vs_baseline": None,
-        "dtype": "int4 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
+        "dtype": "f16", "data": "synthetic",
         "config": {"workload": args.workload, "batch_sizes": spec["ms"],
                    "shapes_NxK": [f"{n}x{k}" for _, n, k in shapes]},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
