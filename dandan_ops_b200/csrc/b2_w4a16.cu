@@ -200,7 +200,7 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.ldx = ldx; a.ldy = ldy;
         a.m = int(rows); a.n = d.n; a.k = d.k;
         a.n16 = d.n16; a.kb = d.kb;
-        a.groups = p.groups; a.max_parts = p.max_parts; a.steps = p.steps;
+        a.groups = p.groups; a.max_parts = p.max_parts; a.steps = int(p.steps);
         int rc;
         switch (p.mt) {
             case 1: rc = launch_stream<1>(a, xvec, p.warps, p.grid, s); break;

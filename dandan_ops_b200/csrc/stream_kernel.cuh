@@ -76,7 +76,7 @@ struct StreamArgs {
     int n16, kb;            // row tiles, column blocks
     int groups;             // row groups = ceil(n16 / W)
     int max_parts;          // partial slots per row tile
-    long long steps;        // groups * kb
+    int steps;              // groups * kb (below 2^20 for every layer the index checks admit)
 };
 
 // ---- small PTX helpers ------------------------------------------------------------------
@@ -142,8 +142,31 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int i) {
     return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
 }
 
+// One 16-byte piece of x: global -> shared without passing through registers (XVEC) so that all
+// pieces of a thread are in flight at once, or assembled from 2-byte loads for unaligned x.
+template <bool XVEC, bool ASYNC = true>
+__device__ __forceinline__ void stage_piece(uint8_t* dst, const __half* src, bool inside, int k, int kmax) {
+    if (!inside) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    } else if constexpr (XVEC && ASYNC) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+    } else if constexpr (XVEC) {
+        *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+    } else {
+        uint32_t h[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            h[e] = (k + e < kmax) ? uint32_t(__half_as_ushort(__ldg(src + e))) : 0u;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(h[0] | h[1] << 16, h[2] | h[3] << 16, h[4] | h[5] << 16, h[6] | h[7] << 16);
+    }
+}
+// Wait for this thread's asynchronous pieces (the caller follows with a block-wide barrier).
+__device__ __forceinline__ void stage_wait() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 // Stage x[0..MT*8) x [k0, k0 + cols) into shared memory (zero beyond M and K).
-template <int MT, bool XVEC, int W>
+template <int MT, bool XVEC, int W, bool WAIT = true>
 __device__ __forceinline__ void stage_x(uint8_t* xs, const StreamArgs& a, int k0, int cols) {
     constexpr int MP = MT * 8;
     constexpr int kThreads = W * 32;
@@ -153,26 +176,15 @@ __device__ __forceinline__ void stage_x(uint8_t* xs, const StreamArgs& a, int k0
         const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
         const int T = cc >> 3, c = cc & 7;
         const int k = k0 + cc * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (m < a.m && k < a.k) {
-            const __half* src = a.x + int64_t(m) * a.ldx + k;
-            if constexpr (XVEC) {
-                v = __ldg(reinterpret_cast<const uint4*>(src));
-            } else {
-                uint32_t h[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    h[e] = (k + e < a.k) ? uint32_t(__half_as_ushort(__ldg(src + e))) : 0u;
-                v = make_uint4(h[0] | h[1] << 16, h[2] | h[3] << 16, h[4] | h[5] << 16, h[6] | h[7] << 16);
-            }
-        }
-        *reinterpret_cast<uint4*>(xs + T * stream_x_chunk_bytes(MP) + m * 144 + c * 16) = v;
+        stage_piece<XVEC>(xs + T * stream_x_chunk_bytes(MP) + m * 144 + c * 16, a.x + int64_t(m) * a.ldx + k,
+                          m < a.m && k < a.k, k, a.k);
     }
+    if constexpr (WAIT) stage_wait();
 }
 
 // Index of the CTA whose range contains step s (ranges are [c*steps/G, (c+1)*steps/G)).
-__device__ __forceinline__ int owner_of(long long s, long long steps, int ctas) {
-    return int(((s + 1) * ctas - 1) / steps);
+__device__ __forceinline__ int owner_of(int s, int steps, int ctas) {
+    return int((unsigned(s + 1) * unsigned(ctas) - 1u) / unsigned(steps));
 }
 
 // MT = number of 8-row tiles of x (1, 2, 4 or 8).  XVEC: x rows are 16-byte aligned and
@@ -191,26 +203,33 @@ w4a16_stream_kernel(const StreamArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int ctas = gridDim.x;
-    const long long b0 = (a.steps * blockIdx.x) / ctas;
-    const long long b1 = (a.steps * (blockIdx.x + 1)) / ctas;
+    // 32-bit step arithmetic: steps * ctas stays below 2^31 (steps < 2^20, at most ~1200 CTAs)
+    const int b0 = int((unsigned(a.steps) * blockIdx.x) / unsigned(ctas));
+    const int b1 = int((unsigned(a.steps) * (blockIdx.x + 1)) / unsigned(ctas));
 
     // This warp's tile exists in every row group except possibly the last one.
     const bool in_last = (a.groups - 1) * kWarps + warp < a.n16;
-    const long long last_start = (long long)(a.groups - 1) * a.kb;
-    const long long wb1 = in_last ? b1 : (b1 < last_start ? b1 : last_start);   // end of this warp's steps
+    const int last_start = (a.groups - 1) * a.kb;
+    const int wb1 = in_last ? b1 : (b1 < last_start ? b1 : last_start);   // end of this warp's steps
 
     const uint32_t bar0 = smem_u32(smem) + warp * kStages * 8;
     uint8_t* ring = smem + kBarBytes + warp * kStages * kBlockBytes;
     const uint32_t ring0 = smem_u32(ring);
     uint8_t* xs = smem + kBarBytes + kRingBytes;
 
+    // When all of K fits in the x buffer it is staged once for the whole kernel: x does not
+    // depend on the row group, so the CTA never has to stop between row groups again.  The
+    // copies are issued first and awaited after the weight requests, so both latencies overlap.
+    const bool whole_x = a.kb <= kPhaseBlocks;
+    if (whole_x) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols);
+
     // Copy-request cursor (used by lane 0): image block (fkb, 16*fgrp + warp).  Consecutive
     // column blocks of one row tile are `stride` bytes apart; at the end of a row group the
     // cursor jumps to the first column block of the next group.
     const long long stride = (long long)a.n16 * kBlockBytes;
-    long long fetch = b0;          // next step to request
+    int fetch = b0;                // next step to request
     int fgrp = int(b0 / a.kb);
-    int fkb = int(b0 - (long long)fgrp * a.kb);
+    int fkb = b0 - fgrp * a.kb;
     const uint8_t* fptr = a.native + ((long long)fkb * a.n16 + fgrp * kWarps + warp) * kBlockBytes;
     auto request = [&](int slot) {
         mbar_expect_tx(bar0 + slot * 8, kBlockBytes);
@@ -238,19 +257,16 @@ w4a16_stream_kernel(const StreamArgs a) {
     uint32_t parity = 0;
     bool failed = false;
 
-    // When all of K fits in the x buffer it is staged once for the whole kernel: x does not
-    // depend on the row group, so the CTA never has to stop between row groups again.
-    const bool whole_x = a.kb <= kPhaseBlocks;
     if (whole_x) {
-        stage_x<MT, XVEC, W>(xs, a, 0, a.kb * kBlockCols);
+        stage_wait();
         __syncthreads();
     }
 
-    long long s0 = b0;
+    int s0 = b0;
     while (s0 < b1) {                                       // one iteration per row group in the range
-        const int grp = int(s0 / a.kb);
-        const int k_lo = int(s0 - (long long)grp * a.kb);
-        const int k_hi = int(min((long long)a.kb, k_lo + (b1 - s0)));
+        const int grp = s0 / a.kb;
+        const int k_lo = s0 - grp * a.kb;
+        const int k_hi = min(a.kb, k_lo + (b1 - s0));
         const int nt = grp * kWarps + warp;
         const bool active = nt < a.n16;
 #pragma unroll
@@ -322,7 +338,7 @@ w4a16_stream_kernel(const StreamArgs a) {
             bool write_out = whole;
             if (!whole) {
                 // Contributors to this row group are the CTAs first..last; mine is slot `blockIdx.x - first`.
-                const long long gs = (long long)grp * a.kb;
+                const int gs = grp * a.kb;
                 const int first = owner_of(gs, a.steps, ctas), last = owner_of(gs + a.kb - 1, a.steps, ctas);
                 const int parts = last - first + 1;
                 // Row groups that are split between CTAs are few: at most one per CTA boundary.

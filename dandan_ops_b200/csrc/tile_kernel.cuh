@@ -70,20 +70,8 @@ w4a16_tile_kernel(const TileArgs a) {
         for (int i = threadIdx.x; i < total; i += blockDim.x) {
             const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
             const int k = cc * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < a.m && k < a.k) {
-                const __half* src = a.x + int64_t(m) * a.ldx + k;
-                if constexpr (XVEC) {
-                    v = __ldg(reinterpret_cast<const uint4*>(src));
-                } else {
-                    uint32_t h[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        h[e] = (k + e < a.k) ? uint32_t(__half_as_ushort(__ldg(src + e))) : 0u;
-                    v = make_uint4(h[0] | h[1] << 16, h[2] | h[3] << 16, h[4] | h[5] << 16, h[6] | h[7] << 16);
-                }
-            }
-            *reinterpret_cast<uint4*>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16) = v;
+            stage_piece<XVEC, false>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16, a.x + int64_t(m) * a.ldx + k,
+                              m < a.m && k < a.k, k, a.k);
         }
     }
     __syncthreads();        // x staged; barrier initialisation visible to every waiter
