@@ -287,16 +287,22 @@ int launch_gemm_one(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cu
     return after_launch("w4a16_gemm_kernel");
 }
 
-// Tile shape of the GEMM: 128 x 128 for at most 128 rows of x, else 256 x 128 or 256 x 192.
-// The wider tile reads x from L2 a third less often, which is what bounds the kernel, but costs
-// about 1.25x per CTA; it is taken when it also needs fewer waves of CTAs over the SMs.
-inline int gemm_ma(int64_t m) { return m <= 128 ? 1 : 2; }
-inline int gemm_bn(int64_t m, int64_t n, int sms) {
-    if (m <= 128) return 128;
-    const int64_t mt = (m + 255) / 256;
-    const int64_t waves128 = (((n + 127) / 128) * mt + sms - 1) / sms;
-    const int64_t waves192 = (((n + 191) / 192) * mt + sms - 1) / sms;
-    return 5 * waves192 < 4 * waves128 ? 192 : 128;
+// Tile shape of the GEMM: (rows of x) x (output columns) = 128 x 128, 256 x 128 or 256 x 192 per CTA.
+// Larger tiles read x from L2 less often - which is what bounds the kernel - but cost more per
+// CTA (about 1.0 : 1.2 : 1.5) and may leave SMs idle; the shape with the cheapest
+// waves x cost-per-CTA wins.
+struct GemmShape { int ma, bn; };
+inline GemmShape gemm_shape(int64_t m, int64_t n, int sms) {
+    if (m <= 128) return {1, 128};
+    const int ma_opt[3] = {1, 2, 2}, bn_opt[3] = {128, 128, 192}, cost[3] = {10, 12, 15};
+    GemmShape best = {2, 128};
+    int64_t best_cost = INT64_MAX;
+    for (int i = 0; i < 3; ++i) {
+        const int64_t ctas = ((n + bn_opt[i] - 1) / bn_opt[i]) * ((m + 128 * ma_opt[i] - 1) / (128 * ma_opt[i]));
+        const int64_t c = ((ctas + sms - 1) / sms) * cost[i];
+        if (c < best_cost) { best_cost = c; best = {ma_opt[i], bn_opt[i]}; }
+    }
+    return best;
 }
 
 int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
@@ -319,7 +325,8 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.status = static_cast<unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1);
     a.ldy = ldy;
     a.m = int(m); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
-    const int ma = gemm_ma(m), bn = gemm_bn(m, d.n, sms);
+    const GemmShape shape = gemm_shape(m, d.n, sms);
+    const int ma = shape.ma, bn = shape.bn;
     const dim3 grid((d.n + bn - 1) / bn, unsigned((m + 128 * ma - 1) / (128 * ma)));
     const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
     if (ma == 1) return vec ? launch_gemm_one<1, 128, true>(map, a, grid, s) : launch_gemm_one<1, 128, false>(map, a, grid, s);
@@ -404,7 +411,8 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
     const b2::Dims d = b2::make_dims(n, k);
     const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
     if (m > B2_STREAM_MAX_M && d.k % 8 == 0) {     // assuming an aligned x, as execution_info cannot see the pointer
-        const int ma = gemm_ma(m), bn = gemm_bn(m, d.n, dev.sm_count > 0 ? dev.sm_count : 148);
+        const GemmShape shape = gemm_shape(m, d.n, dev.sm_count > 0 ? dev.sm_count : 148);
+        const int ma = shape.ma, bn = shape.bn;
         if (route) *route = B2_ROUTE_TCGEN05;
         if (k_splits) *k_splits = 1;
         if (grid) *grid = ((d.n + bn - 1) / bn) * int((m + 128 * ma - 1) / (128 * ma));
