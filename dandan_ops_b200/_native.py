@@ -35,6 +35,7 @@ _SIGNATURES = {
     "b2_w4a16_linear": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b2_w4a16_linear_static": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "b2_w4a16_linear_route": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
+    "b2_w4a16_linear_bias": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_plan": (_int, [_i64, _i64, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int),
                              ctypes.POINTER(_int), ctypes.POINTER(_int)]),
 }
@@ -185,14 +186,14 @@ def linear_static(x, image, n, k, out):
 _need_cache = {}
 
 
-def linear(x, image, n, k, route=ROUTE_AUTO, out=None):
-    """y[M,N] = x[M,K] @ W^T on the current stream.  x must be CUDA FP16 with unit inner stride."""
+def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
+    """y[M,N] = x[M,K] @ W^T (+ FP16 bias [N]) on the current stream.  x must be CUDA FP16 with unit inner stride."""
     lib = _lib if _lib is not None else load()
     m = x.shape[0]
     device = x.device
     if torch.cuda.current_device() != device.index:      # rare: keep the common path free of context switches
         with torch.cuda.device(device):
-            return linear(x, image, n, k, route, out)
+            return linear(x, image, n, k, route, out, bias)
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=device)
     if m == 0:
         return y
@@ -204,8 +205,9 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None):
     ws = _workspaces.get((device.index, stream))
     if ws is None or ws.numel() < need:
         ws = workspace(device, need)
-    rc = lib.b2_w4a16_linear_route(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(), y.data_ptr(),
-                                   y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream, route)
+    rc = lib.b2_w4a16_linear_bias(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
+                                  bias.data_ptr() if bias is not None else None, y.data_ptr(),
+                                  y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream, route)
     if rc != OK:
         _check(rc)
     return y

@@ -165,12 +165,13 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 }
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
-             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s) {
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias) {
     b2::TileArgs a;
     a.x = static_cast<const __half*>(x);
     a.native = static_cast<const uint8_t*>(native);
     a.y = static_cast<__half*>(y);
     a.status = workspace ? static_cast<unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1) : nullptr;
+    a.bias = static_cast<const __half*>(bias);
     a.ldx = ldx; a.ldy = ldy;
     a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
     a.warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
@@ -182,7 +183,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
                const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s,
-               const DeviceInfo& dev) {
+               const DeviceInfo& dev, const void* bias) {
     const int64_t ticket_bytes = B2_W4A16_TICKET_BYTES;
     const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
     for (int64_t m0 = 0; m0 < m; m0 += B2_STREAM_MAX_M) {
@@ -196,6 +197,7 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.y = static_cast<__half*>(y) + m0 * ldy;
         a.ticket = static_cast<unsigned*>(workspace);
         a.status = a.ticket + (B2_W4A16_TICKET_BYTES / 4 - 1);
+        a.bias = static_cast<const __half*>(bias);
         a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ticket_bytes);
         a.ldx = ldx; a.ldy = ldy;
         a.m = int(rows); a.n = d.n; a.k = d.k;
@@ -306,7 +308,7 @@ inline GemmShape gemm_shape(int64_t m, int64_t n, int sms) {
 }
 
 int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
-             const b2::Dims& d, void* workspace, cudaStream_t s, int sms) {
+             const b2::Dims& d, void* workspace, cudaStream_t s, int sms, const void* bias) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return fail(B2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
     if (workspace == nullptr) return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
@@ -323,6 +325,7 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.native = static_cast<const uint8_t*>(native);
     a.y = static_cast<__half*>(y);
     a.status = static_cast<unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1);
+    a.bias = static_cast<const __half*>(bias);
     a.ldy = ldy;
     a.m = int(m); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
     const GemmShape shape = gemm_shape(m, d.n, sms);
@@ -450,9 +453,11 @@ int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     return stream_workspace_bytes(m > 0 ? m : 1, b2::make_dims(n, k), dev.sm_count);
 }
 
-int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
-                          int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes,
-                          void* stream, int route) {
+int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                         int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                         int64_t workspace_bytes, void* stream, int route) {
+    const void* bias = bias_fp16;
+    if (bias && reinterpret_cast<uintptr_t>(bias) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
     if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
     if (int rc = check_dims(n, k)) return rc;
     if (m == 0) return B2_OK;
@@ -476,19 +481,25 @@ int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* 
         if (!tile_applicable(m, d))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
-        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream));
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias);
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
-                          static_cast<cudaStream_t>(stream), dev);
+                          static_cast<cudaStream_t>(stream), dev, bias);
     if (route == B2_ROUTE_TCGEN05) {
         if (!gemm_applicable(x, ldx, d))
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
         if (workspace_bytes < B2_W4A16_TICKET_BYTES)
             return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
-        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, static_cast<cudaStream_t>(stream), dev.sm_count);
+        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, static_cast<cudaStream_t>(stream), dev.sm_count, bias);
     }
     return fail(B2_ERR_UNSUPPORTED, "unknown route");
+}
+
+int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,
+                          int64_t m, int64_t n, int64_t k, void* workspace, int64_t workspace_bytes,
+                          void* stream, int route) {
+    return b2_w4a16_linear_bias(x, ldx, native, nullptr, y, ldy, m, n, k, workspace, workspace_bytes, stream, route);
 }
 
 int b2_w4a16_linear_static(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,

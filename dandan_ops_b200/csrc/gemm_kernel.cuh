@@ -57,6 +57,7 @@ struct GemmArgs {
     const uint8_t* native;
     __half* y;
     unsigned* status;
+    const __half* bias;     // optional [N] FP16 (may be null)
     int64_t ldy;
     int m, n, k;
     int n16, kb;
@@ -284,6 +285,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     __half2 hh = __floats2half2_rn(__uint_as_float(v[q * 8 + 2 * e]), __uint_as_float(v[q * 8 + 2 * e + 1]));
+                                    if (a.bias) hh = __hadd2(hh, *reinterpret_cast<const __half2*>(a.bias + n0 + q * 8 + 2 * e));
                                     p[e] = *reinterpret_cast<uint32_t*>(&hh);
                                 }
                                 *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(p[0], p[1], p[2], p[3]);
@@ -291,7 +293,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
                         } else {
 #pragma unroll
                             for (int e = 0; e < 32; ++e)
-                                if (n0 + e < a.n) dst[e] = __float2half_rn(__uint_as_float(v[e]));
+                                if (n0 + e < a.n) dst[e] = finish_output(__uint_as_float(v[e]), a.bias, n0 + e);
                         }
                     }
                 }

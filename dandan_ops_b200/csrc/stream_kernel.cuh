@@ -71,6 +71,7 @@ struct StreamArgs {
     float* partial;         // [split tile][max_parts][MT][32 lanes][4]
     unsigned* ticket;       // [split tile], zero on entry and on exit
     unsigned* status;       // sticky error word (0 = ok)
+    const __half* bias;     // optional [N] FP16, added to the FP16-rounded product (may be null)
     int64_t ldx, ldy;
     int m, n, k;
     int n16, kb;            // row tiles, column blocks
@@ -107,6 +108,12 @@ __device__ __forceinline__ void fma_mixed_16th(uint32_t h2, float c, float& lo, 
     asm("{\n\t.reg .b16 l, h, s;\n\tmov.b32 {l, h}, %2;\n\tmov.b16 s, 0x2C00;\n\t"
         "fma.rn.f32.f16 %0, l, s, %3;\n\tfma.rn.f32.f16 %1, h, s, %3;\n\t}"
         : "=f"(lo), "=f"(hi) : "r"(h2), "f"(c));
+}
+// The output rounding of every linear kernel: FP16(acc), then the FP16 bias added in FP16
+// (the reference rounds the product first and adds bias.to(fp16) afterwards).
+__device__ __forceinline__ __half finish_output(float acc, const __half* bias, int n) {
+    const __half h = __float2half_rn(acc);
+    return bias ? __hadd(h, bias[n]) : h;
 }
 // (lo*s, hi*s) rounded to an FP16 pair; each multiply is one IEEE FP32 rounding.
 __device__ __forceinline__ uint32_t scale_pack(float lo, float hi, float s) {
@@ -379,7 +386,7 @@ w4a16_stream_kernel(const StreamArgs a) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int m = m0 + (c & 1), n = n0 + 8 * (c >> 1);
-                        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = __float2half_rn(acc[mt][c]);
+                        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(acc[mt][c], a.bias, n);
                     }
                 }
             }

@@ -26,6 +26,7 @@ struct TileArgs {
     const uint8_t* native;
     __half* y;
     unsigned* status;       // may be null
+    const __half* bias;     // optional [N] FP16 (may be null)
     int64_t ldx, ldy;
     int m, n, k;
     int n16, kb;
@@ -138,7 +139,7 @@ w4a16_tile_kernel(const TileArgs a) {
             sum += reinterpret_cast<const float*>(red)[((w * MT + mt) * 32 + rl) * 4 + c];
         const int rg = rl >> 2, rt = rl & 3;
         const int m = mt * 8 + 2 * rt + (c & 1), n = nt * 16 + rg + 8 * (c >> 1);
-        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = __float2half_rn(sum);
+        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(sum, a.bias, n);
     }
 }
 

@@ -81,12 +81,12 @@ def _image_for(packed, scales, zeros, in_features):
     return image
 
 
-def _engine(x, image, rows, in_features, bias):
+def _engine(x, image, rows, in_features, bias16):
+    """`bias16`: the bias already converted to FP16 (or None).  The kernels round the product to
+    FP16 first and add the FP16 bias afterwards, as the reference's `y + bias.to(y.dtype)` does."""
     if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < in_features):
         x = x.contiguous()
-    y = _native.linear(x, image, rows, in_features)
-    # The reference rounds the product to FP16 first and adds the FP16 bias afterwards.
-    return y if bias is None else y + bias.to(y.dtype)
+    return _native.linear(x, image, rows, in_features, bias=bias16)
 
 
 def quantized_linear(x, packed_weight, scales, zeros, *, in_features, group_size=64, bias=None,
@@ -103,7 +103,8 @@ def quantized_linear(x, packed_weight, scales, zeros, *, in_features, group_size
     _check_bias(bias, packed_weight.shape[0], x.device)
     _resolve(x, scales, group_size, backend)
     image = _image_for(packed_weight.contiguous(), scales.contiguous(), zeros.contiguous(), in_features)
-    return _engine(x, image, packed_weight.shape[0], in_features, bias)
+    bias16 = None if bias is None else bias.to(torch.float16).contiguous()
+    return _engine(x, image, packed_weight.shape[0], in_features, bias16)
 
 
 class QuantizedLinear(torch.nn.Module):
@@ -131,6 +132,8 @@ class QuantizedLinear(torch.nn.Module):
         self.register_buffer("bias", None if bias is None else bias.detach().clone().contiguous())
         self._image = None
         self._image_key = None
+        self._bias16 = None
+        self._bias16_key = None
         self.eval()
         if self.packed_weight.is_cuda and group_size == 64:
             self._native_image()
@@ -212,6 +215,16 @@ class QuantizedLinear(torch.nn.Module):
             self._image_key = key
         return self._image
 
+    def _bias_fp16(self):
+        """FP16 copy of the bias for the fused epilogue (derived, rebuilt when the bias changes)."""
+        if self.bias is None:
+            return None
+        key = (self.bias.data_ptr(), self.bias._version, self.bias.dtype)
+        if self._bias16 is None or self._bias16_key != key:
+            self._bias16 = self.bias.detach().to(torch.float16).contiguous()
+            self._bias16_key = key
+        return self._bias16
+
     # -- introspection ---------------------------------------------------------------------
     def execution_info(self, x):
         """What `forward(x)` would run, without running it (same keys as the reference;
@@ -257,4 +270,4 @@ class QuantizedLinear(torch.nn.Module):
             raise ValueError("x and quantized weight must share a device")
         _check_bias(self.bias, self.out_features, x.device)
         _resolve(x, self.scales, self.group_size, self.backend)
-        return _engine(x, self._native_image(), self.out_features, self.in_features, self.bias)
+        return _engine(x, self._native_image(), self.out_features, self.in_features, self._bias_fp16())

@@ -146,6 +146,14 @@ int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* 
                           int64_t m, int64_t n, int64_t k, void* workspace,
                           int64_t workspace_bytes, void* stream, int route);
 
+/* y = fp16(x @ W^T) + bias, the bias add fused into the kernels' output stage with the
+ * reference's rounding order: the product is rounded to FP16 first, then the FP16 bias is added
+ * in FP16 (`y + bias.to(y.dtype)`, dandan_ops/quantized_linear.py:81, a separate elementwise
+ * launch there).  `bias_fp16` is [N] FP16, 4-byte aligned, or NULL for no bias. */
+int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                         int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                         int64_t workspace_bytes, void* stream, int route);
+
 /* Which kernel family B2_ROUTE_AUTO picks for this problem (a B2_ROUTE_* value) and,
  * through the optional out-parameters, the launch plan: K-splits, grid size, rows of x
  * handled per launch.  Pure host arithmetic; used by execution_info(). */

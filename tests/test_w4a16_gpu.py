@@ -361,3 +361,20 @@ def test_route_limits_are_reported():
                        route=_native.ROUTE_TILE)
     with pytest.raises(RuntimeError, match="route"):
         _native.linear(torch.zeros(1, 512, dtype=torch.float16, device="cuda"), image, 64, 512, route=9)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1000, 1024), (8, 67, 129), (16, 4096, 1024), (40, 1001, 520), (8, 6144, 4096),
+                                   (300, 1000, 1024), (129, 130, 264), (512, 4104, 1024)])
+@pytest.mark.parametrize("bias_dtype", [torch.float32, torch.float16])
+def test_fused_bias_keeps_the_reference_rounding_order(m, n, k, bias_dtype):
+    g = torch.Generator().manual_seed(m + 3 * n + k)
+    bias = (torch.randn(n, generator=g) * 3).to(bias_dtype).cuda()
+    layer = ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.04).half().cuda(), bias)
+    x = torch.randn(m, k, generator=g).half().cuda()
+    plain = _native.linear(x, layer._native_image(), n, k)            # product only
+    y = layer(x)
+    assert torch.equal(y, plain + bias.to(torch.float16))             # bit-exact: fp16(product) + fp16(bias)
+    assert torch.equal(ops.quantized_linear(x, layer.packed_weight, layer.scales, layer.zeros, in_features=k,
+                                            bias=bias), y)
+    layer.bias.mul_(2)                                                 # in-place change is picked up
+    assert torch.equal(layer(x), plain + (bias * 2).to(torch.float16))
