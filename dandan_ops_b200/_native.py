@@ -13,6 +13,7 @@ from . import build as _build
 OK = 0
 ROUTE_AUTO, ROUTE_STREAM, ROUTE_TCGEN05, ROUTE_TILE = 0, 1, 2, 3
 ROUTE_NAMES = {ROUTE_STREAM: "b200_stream", ROUTE_TCGEN05: "b200_tcgen05", ROUTE_TILE: "b200_tile"}
+GEMM_SHAPES = {"auto": 0, "128x128": 1, "256x128": 2, "256x192": 3, "pair256": 4, "pair192": 5}
 STREAM_MAX_M = 64
 TICKET_BYTES = 16384
 
@@ -24,6 +25,7 @@ _SIGNATURES = {
     "b2_w4a16_contract_version": (_int, []),
     "b2_w4a16_last_error": (ctypes.c_char_p, []),
     "b2_w4a16_launch_count": (_i64, []),
+    "b2_w4a16_set_gemm_shape": (_int, [_int]),
     "b2_w4a16_native_bytes": (_i64, [_i64, _i64]),
     "b2_w4a16_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "b2_w4a16_unrepack": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
@@ -79,6 +81,12 @@ def _stream():
 
 def launch_count():
     return int(load().b2_w4a16_launch_count())
+
+
+def set_gemm_shape(name="auto"):
+    """Force one tile shape of the tensor-memory GEMM for every later call (tests, tuning);
+    "auto" restores the per-call cost model."""
+    _check(load().b2_w4a16_set_gemm_shape(GEMM_SHAPES[name]))
 
 
 def native_bytes(n, k):

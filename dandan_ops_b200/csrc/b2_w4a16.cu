@@ -12,6 +12,7 @@
 #include "layout_kernels.cuh"
 #include "stream_kernel.cuh"
 #include "gemm_kernel.cuh"
+#include "gemm_pair_kernel.cuh"
 #include "tile_kernel.cuh"
 
 namespace {
@@ -289,20 +290,65 @@ int launch_gemm_one(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cu
     return after_launch("w4a16_gemm_kernel");
 }
 
-// Tile shape of the GEMM: (rows of x) x (output columns) = 128 x 128, 256 x 128 or 256 x 192 per CTA.
-// Larger tiles read x from L2 less often - which is what bounds the kernel - but cost more per
-// CTA (about 1.0 : 1.2 : 1.5) and may leave SMs idle; the shape with the cheapest
-// waves x cost-per-CTA wins.
-struct GemmShape { int ma, bn; };
+template <int MT>
+int launch_gemm_pair(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_gemm_pair_kernel<MT>;
+    constexpr int smem = b2::pair_smem_bytes<MT>();
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<grid, b2::kPairThreads, smem, s>>>(map, a);   // clusters of two along x (__cluster_dims__)
+    return after_launch("w4a16_gemm_pair_kernel");
+}
+
+// Tile shapes of the GEMM.  Single-CTA kernel: (rows of x) x (output columns) = 128 x 128,
+// 256 x 128 or 256 x 192 per CTA.  Pair kernel: 256 output columns x 256 rows of x per two SMs
+// (one CTA per SM), or x 192 rows with two CTAs per SM.  The cost of one tile per SM, measured on
+// large layers, is about 10 : 12 : 15 for the single-CTA shapes and 9 / 6.75 for the pair shapes
+// (the pair kernel is ~10 % cheaper per multiply-add); the shape with the cheapest
+// waves x cost-per-tile wins.  With two co-resident CTAs a wave costs two units, a last wave that
+// fills at most half of the slots one.
+struct GemmShape {
+    int ma, bn;      // single-CTA kernel: accumulators of 128 x rows, output columns
+    int pair_mt;     // pair kernel: rows of x per CTA pair (256 or 192), 0 = single-CTA kernel
+    int64_t ctas(int64_t m, int64_t n) const {
+        if (pair_mt) return 2 * ((n + 255) / 256) * ((m + pair_mt - 1) / pair_mt);
+        return ((n + bn - 1) / bn) * ((m + 128 * ma - 1) / (128 * ma));
+    }
+};
+constexpr GemmShape kGemmShapes[5] = {{1, 128, 0}, {2, 128, 0}, {2, 192, 0}, {0, 0, 256}, {0, 0, 192}};
+std::atomic<int> g_forced_shape{0};      // B2_GEMM_SHAPE_*, 0 = automatic
+
 inline GemmShape gemm_shape(int64_t m, int64_t n, int sms) {
-    if (m <= 128) return {1, 128};
-    const int ma_opt[3] = {1, 2, 2}, bn_opt[3] = {128, 128, 192}, cost[3] = {10, 12, 15};
-    GemmShape best = {2, 128};
+    const int forced = g_forced_shape.load(std::memory_order_relaxed);
+    if (forced >= 1 && forced <= 5) return kGemmShapes[forced - 1];
+    if (m <= 128) return kGemmShapes[0];
+    const int cost4[5] = {40, 48, 60, 36, 27};           // cost per tile and SM, times four
+    const int64_t pairs = sms >= 2 ? sms / 2 : 1;
+    GemmShape best = kGemmShapes[1];
     int64_t best_cost = INT64_MAX;
-    for (int i = 0; i < 3; ++i) {
-        const int64_t ctas = ((n + bn_opt[i] - 1) / bn_opt[i]) * ((m + 128 * ma_opt[i] - 1) / (128 * ma_opt[i]));
-        const int64_t c = ((ctas + sms - 1) / sms) * cost[i];
-        if (c < best_cost) { best_cost = c; best = {ma_opt[i], bn_opt[i]}; }
+    for (int i = 0; i < 5; ++i) {
+        const GemmShape& g = kGemmShapes[i];
+        int64_t units;
+        if (g.pair_mt == 0) {
+            units = (g.ctas(m, n) + sms - 1) / sms;
+        } else {
+            const int64_t tiles = g.ctas(m, n) / 2;
+            if (g.pair_mt == 256) {
+                units = (tiles + pairs - 1) / pairs;
+            } else {
+                const int64_t rem = tiles % (2 * pairs);
+                units = 2 * (tiles / (2 * pairs)) + (rem == 0 ? 0 : rem <= pairs ? 1 : 2);
+            }
+        }
+        const int64_t c = units * cost4[i];
+        if (c < best_cost) { best_cost = c; best = g; }
     }
     return best;
 }
@@ -315,7 +361,9 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(m)};
     const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
-    const cuuint32_t box[2] = {cuuint32_t(b2::kGemmBK), 128};
+    const GemmShape shape = gemm_shape(m, d.n, sms);
+    const int pair_mt = shape.pair_mt;
+    const cuuint32_t box[2] = {cuuint32_t(b2::kGemmBK), pair_mt ? cuuint32_t(pair_mt / 2) : 128u};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -328,10 +376,13 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.bias = static_cast<const __half*>(bias);
     a.ldy = ldy;
     a.m = int(m); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
-    const GemmShape shape = gemm_shape(m, d.n, sms);
+    const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
+    if (pair_mt) {
+        const dim3 pgrid(2 * unsigned((d.n + 255) / 256), unsigned((m + pair_mt - 1) / pair_mt));
+        return pair_mt == 256 ? launch_gemm_pair<256>(map, a, pgrid, s) : launch_gemm_pair<192>(map, a, pgrid, s);
+    }
     const int ma = shape.ma, bn = shape.bn;
     const dim3 grid((d.n + bn - 1) / bn, unsigned((m + 128 * ma - 1) / (128 * ma)));
-    const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
     if (ma == 1) return vec ? launch_gemm_one<1, 128, true>(map, a, grid, s) : launch_gemm_one<1, 128, false>(map, a, grid, s);
     if (bn == 128) return vec ? launch_gemm_one<2, 128, true>(map, a, grid, s) : launch_gemm_one<2, 128, false>(map, a, grid, s);
     return vec ? launch_gemm_one<2, 192, true>(map, a, grid, s) : launch_gemm_one<2, 192, false>(map, a, grid, s);
@@ -346,6 +397,13 @@ int b2_w4a16_contract_version(void) { return 2; }
 const char* b2_w4a16_last_error(void) { return g_error.c_str(); }
 
 int64_t b2_w4a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b2_w4a16_set_gemm_shape(int shape) {
+    if (shape < B2_GEMM_SHAPE_AUTO || shape > B2_GEMM_SHAPE_PAIR_192)
+        return fail(B2_ERR_ARGUMENT, "unknown GEMM tile shape");
+    g_forced_shape.store(shape, std::memory_order_relaxed);
+    return B2_OK;
+}
 
 int64_t b2_w4a16_native_bytes(int64_t n, int64_t k) {
     if (check_dims(n, k) != B2_OK) return 0;
@@ -415,10 +473,9 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
     const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
     if (m > B2_STREAM_MAX_M && d.k % 8 == 0) {     // assuming an aligned x, as execution_info cannot see the pointer
         const GemmShape shape = gemm_shape(m, d.n, dev.sm_count > 0 ? dev.sm_count : 148);
-        const int ma = shape.ma, bn = shape.bn;
         if (route) *route = B2_ROUTE_TCGEN05;
         if (k_splits) *k_splits = 1;
-        if (grid) *grid = ((d.n + bn - 1) / bn) * int((m + 128 * ma - 1) / (128 * ma));
+        if (grid) *grid = int(shape.ctas(m, d.n));
         if (rows_per_launch) *rows_per_launch = int(m);
         return B2_OK;
     }

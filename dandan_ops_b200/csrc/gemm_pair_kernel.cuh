@@ -1,0 +1,296 @@
+// Prefill kernel for large batches: two CTAs on neighbouring SMs (a cluster of two) compute a
+// tile of 256 output columns (weight rows) by 256 rows of x with one
+// tcgen05.mma.cta_group::2 instruction stream, the dequantized weights going through tensor
+// memory instead of shared memory.
+//
+//   D[n][m] (FP32, tensor memory: 128 lanes = this CTA's weight rows, 256 columns = x rows)
+//     += A[n][k] (weights, FP16, written to tensor memory by the converter warps: tcgen05.st)
+//      * B[m][k] (x tile, FP16, shared memory, TMA with the 128-byte swizzle; each CTA loads
+//                 128 of the 256 rows and the tensor cores of both SMs read both halves)
+//
+// Why this shape: per 64-column step a CTA's shared memory only takes the 16 KB x tile once
+// from TMA and once into the tensor core, plus the 4.6 KB of raw 4-bit blocks - the FP16 weight
+// tile (16 KB written, 16 KB read per step in the single-CTA kernel, which made shared-memory
+// bandwidth the limit there) never touches it.  Every weight is converted once per 256 rows
+// of x, every x byte is fetched from L2 once per 256 output columns, and eight x stages
+// (128 KB) cover the TMA latency under load.
+//
+// Roles per CTA (10 warps):
+//   warp 0      copy producer: bulk copies of this CTA's 8 native blocks per 256 columns of K,
+//               TMA loads of this CTA's x rows; the loads of BOTH CTAs complete the leader's
+//               x_full barrier (cp.async.bulk.tensor with .cta_group::2)
+//   warp 1      allocates/frees tensor memory (cta_group::2, both CTAs); in the leader CTA
+//               (cluster rank 0) one lane issues the MMAs and commits to the barriers of both CTAs
+//   warps 2..9  converters: thread = weight row (tensor-memory lane), two warps per lane
+//               quadrant, 32 of the step's 64 columns each; afterwards the epilogue
+//               (tcgen05.ld -> FP16 (+bias) -> y, transposed: a warp stores 32 consecutive
+//               output columns of one row of y per instruction)
+//
+// Barriers (every wait is bounded, as in the single-CTA kernel):
+//   raw_full/raw_free[r]   local: bulk copy done / all converter warps finished with raw stage r
+//   x_full[s]              leader only: transaction bytes of both CTAs' x loads
+//   w_full[s]              leader only: one arrival per converter warp of both CTAs
+//   x_free[s], w_free[s]   both CTAs: tcgen05.commit (multicast) after the MMAs that read stage s
+//   acc_full               both CTAs: tcgen05.commit after the last MMA
+#pragma once
+#include "gemm_kernel.cuh"
+
+namespace b2 {
+
+constexpr int kPairRows = 128;                                   // weight rows per CTA (256 per pair)
+constexpr int kPairConverters = 8;                               // converter warps per CTA
+constexpr int kPairThreads = 64 + 32 * kPairConverters;
+constexpr int kPairRawBytes = (kPairRows / 16) * kBlockBytes;    // 18688: 8 native blocks
+constexpr uint32_t kPairWCols = kGemmBK / 2;                     // 32 columns hold 64 FP16 of a weight row
+// Two shapes.  MT = rows of x per pair (the MMA's N; each CTA loads MT/2 of them):
+//   MT = 256: one CTA per SM, 8 x stages, 4 weight stages, 512 tensor-memory columns
+//   MT = 192: two CTAs per SM (each half the shared memory and 256 columns), so that one pair's
+//             prologue and epilogue overlap the other pair's main loop
+template <int MT> struct PairShape;
+template <> struct PairShape<256> { static constexpr int XS = 8, WS = 4, RS = 3, CTAS = 1; };
+template <> struct PairShape<192> { static constexpr int XS = 5, WS = 2, RS = 2, CTAS = 2; };
+__host__ __device__ constexpr int pair_x_bytes(int mt) { return (mt / 2) * kGemmBK * 2; }
+template <int MT> __host__ __device__ constexpr int pair_smem_bytes() {
+    return 1024 + PairShape<MT>::XS * pair_x_bytes(MT) + PairShape<MT>::RS * kPairRawBytes + 512;
+}
+template <int MT> __host__ __device__ constexpr uint32_t pair_tmem_cols() { return MT + PairShape<MT>::WS * kPairWCols <= 256 ? 256 : 512; }
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in the CTA with the given cluster rank.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrival on a barrier that may live in the peer CTA.  CTA-scope release: the data the arrival
+// publishes is in tensor memory (ordered by tcgen05.wait::st and the tcgen05 fences), and a
+// cluster-scope release costs a device-wide memory barrier per arrival.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// x tile load whose completion bytes go to a barrier that may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor], issued for both SMs of the pair.
+__device__ __forceinline__ void umma_f16_pair_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs once all earlier MMAs have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+                 "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
+                 ::"r"(bar) : "memory");
+}
+// 16 registers -> 16 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int MT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, PairShape<MT>::CTAS)
+w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
+    constexpr int XS = PairShape<MT>::XS, WS = PairShape<MT>::WS, RS = PairShape<MT>::RS;
+    constexpr int kXBytes = pair_x_bytes(MT);
+    constexpr uint32_t kTmemCols = pair_tmem_cols<MT>();
+    static_assert(WS <= XS && MT % 64 == 0, "one barrier ring serves both operand rings");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* x_base = smem;                                                // [XS][kXBytes]
+    uint8_t* raw_base = x_base + XS * kXBytes;                             // [RS][18688]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw_base + RS * kPairRawBytes);
+    // FULL[s % XS] (leader): the x bytes of both CTAs and every converter warp's weights of step s
+    // are in place.  DONE[s % XS] (both CTAs): the MMAs of step s have completed.
+    constexpr int RAW_FULL = 0, RAW_FREE = RAW_FULL + RS, FULL = RAW_FREE + RS, DONE = FULL + XS,
+                  ACC_FULL = DONE + XS, NBARS = ACC_FULL + 1;
+    static_assert(NBARS * 8 + 8 <= 512, "barrier area");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + i * 8; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int tile_n = blockIdx.x >> 1, tile_m = blockIdx.y;
+    const int m0 = tile_m * MT;                                            // first x row of the pair
+    const int n0 = tile_n * (2 * kPairRows) + int(rank) * kPairRows;       // first weight row of this CTA
+    const int ksteps = (a.k + kGemmBK - 1) / kGemmBK;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < RS; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_FREE + i), kPairConverters); }
+        for (int i = 0; i < XS; ++i) { mbar_init(bar(FULL + i), 1 + 2 * kPairConverters); mbar_init(bar(DONE + i), 1); }
+        mbar_init(bar(ACC_FULL), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tcgen05_fence_before();
+    cluster_sync_all();                     // barriers of both CTAs exist before any remote arrival
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_w = tmem_base + MT;                                // weight ring behind the accumulator
+
+    auto give_up = [&]() {
+        *abort_flag = 1;
+        atomicOr(a.status, kStatusGemmTimeout);
+    };
+    auto wait = [&](int idx, uint32_t parity) -> bool {
+        for (int i = 0; i < kWaitLimit; ++i) {
+            if (mbar_try_wait(bar(idx), parity)) return true;
+            if ((i & 63) == 63 && *abort_flag) return false;
+        }
+        give_up();
+        return false;
+    };
+
+    if (warp == 0) {
+        // ------------------------------ copy producer ------------------------------------
+        if (lane == 0) {
+            const int nt0 = n0 >> 4;
+            const int blocks_here = max(0, min(kPairRows / 16, a.n16 - nt0));
+            const uint32_t raw_bytes = uint32_t(blocks_here) * kBlockBytes;
+            const uint8_t* src = a.native + int64_t(nt0) * kBlockBytes;
+            const int64_t stride = int64_t(a.n16) * kBlockBytes;
+            const uint32_t full_leader = map_to_cta(bar(FULL), 0);
+            for (int s = 0; s < ksteps; ++s) {
+                if ((s & 3) == 0) {
+                    const int kb = s >> 2, r = kb % RS;
+                    if (kb >= RS && !wait(RAW_FREE + r, ((kb / RS) - 1) & 1)) break;
+                    if (raw_bytes) {
+                        mbar_expect_tx(bar(RAW_FULL + r), raw_bytes);
+                        bulk_copy_g2s(smem_u32(raw_base + r * kPairRawBytes), src + kb * stride, raw_bytes, bar(RAW_FULL + r));
+                    } else {
+                        mbar_arrive(bar(RAW_FULL + r));       // no weight rows here: columns beyond N, masked in the epilogue
+                    }
+                }
+                const int st = s % XS;
+                if (s >= XS && !wait(DONE + st, ((s / XS) - 1) & 1)) break;
+                if (leader) mbar_expect_tx(bar(FULL + st), 2 * kXBytes);
+                tma_load_2d_pair(smem_u32(x_base + st * kXBytes), &xmap, s * kGemmBK, m0 + int(rank) * (MT / 2), full_leader + st * 8);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (one lane of the leader CTA) -----------
+        if (leader && lane == 0) {
+            // D = F32, A = B = F16, both K-major, M = 256 weight rows, N = MT rows of x
+            const uint32_t idesc = (1u << 4) | (uint32_t(MT >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+            const uint64_t desc0 = umma_desc_sw128(smem_u32(x_base));
+            bool have = false;                  // the coming step's barrier was already seen complete
+            int xs = 0, ws = 0;
+            uint32_t par = 0;
+            for (int s = 0; s < ksteps; ++s) {
+                if (!have && !wait(FULL + xs, par)) break;
+                tcgen05_fence_after();
+                const uint64_t desc = desc0 + uint64_t((xs * kXBytes) >> 4);
+                const uint32_t w_addr = tmem_w + ws * kPairWCols;
+                const int xn = xs + 1 == XS ? 0 : xs + 1;
+                const uint32_t parn = xs + 1 == XS ? par ^ 1 : par;
+#pragma unroll
+                for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                    // look at the next step's barrier while the tensor cores still have work queued
+                    if (kk == kGemmBK / 16 - 1) have = s + 1 < ksteps && mbar_try_wait(bar(FULL + xn), parn);
+                    umma_f16_pair_ts(tmem_base, w_addr + kk * 8, desc + uint64_t(kk * 2), idesc, (s > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit_pair(bar(DONE + xs));
+                if (s == ksteps - 1) umma_commit_pair(bar(ACC_FULL));
+                xs = xn; par = parn;
+                ws = ws + 1 == WS ? 0 : ws + 1;
+            }
+        }
+    } else {
+        // ------------------------------ converters ---------------------------------------
+        const int quad = warp & 3;                      // tensor-memory lane quadrant this warp may access
+        const int half = (warp - 2) >> 2;               // which 32 of the step's 64 columns
+        const int r = quad * 32 + lane;                 // weight row of this CTA = tensor-memory lane
+        const int blk = r >> 4, rr = r & 15, g = rr & 7, hi8 = rr >> 3;
+        const uint32_t full_leader = map_to_cta(bar(FULL), 0);
+        const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+        bool ok = true;
+        for (int s = 0; s < ksteps && ok; ++s) {
+            const int kb = s >> 2, t = s & 3, rs = kb % RS;
+            if (t == 0) ok = wait(RAW_FULL + rs, (kb / RS) & 1);
+            if (!ok) break;
+            const uint8_t* nb = raw_base + rs * kPairRawBytes + blk * kBlockBytes;
+            const int lane_idx = 4 * g + t;
+            const uint4 code = *reinterpret_cast<const uint4*>(nb + (2 * hi8 + half) * 512 + lane_idx * 16);
+            const float step = *reinterpret_cast<const float*>(nb + kStepOffset + (lane_idx * 2 + hi8) * 4);
+            const float z = float((nb[kZeroOffset + lane_idx] >> (4 * hi8)) & 15);
+            const float c_even = -(1024.0f + z), c_odd = -(64.0f + z);
+            const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 q = dequant_word(words[i], c_even, c_odd, step);
+                o[4 * i] = q.x; o[4 * i + 1] = q.y; o[4 * i + 2] = q.z; o[4 * i + 3] = q.w;
+            }
+            // the conversion happens in registers before the wait for the free tensor-memory stage
+            if (s >= WS) ok = wait(DONE + (s - WS) % XS, ((s - WS) / XS) & 1);
+            if (!ok) break;
+            tcgen05_fence_after();
+            tmem_st16(tmem_w + lane_addr + (s % WS) * kPairWCols + half * 16, o);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(full_leader + (s % XS) * 8);
+                if (t == 3 || s == ksteps - 1) mbar_arrive(bar(RAW_FREE + rs));
+            }
+        }
+        // ------------------------------ epilogue -----------------------------------------
+        if (ok && wait(ACC_FULL, 0)) {
+            tcgen05_fence_after();
+            const int n = n0 + r;
+            const bool n_ok = n < a.n;
+            const __half bias = (a.bias && n_ok) ? a.bias[n] : __float2half(0.0f);
+#pragma unroll 1
+            for (int cc = 0; cc < MT / 64; ++cc) {
+                const int col = half * (MT / 2) + cc * 32;           // x rows col .. col+31 of the pair tile
+                uint32_t v[32];
+                tmem_ld32(tmem_base + lane_addr + col, v);
+                if (n_ok) {
+                    __half* dst = a.y + int64_t(m0 + col) * a.ldy + n;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        if (m0 + col + e < a.m) {
+                            __half hv = __float2half_rn(__uint_as_float(v[e]));
+                            if (a.bias) hv = __hadd(hv, bias);
+                            dst[int64_t(e) * a.ldy] = hv;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // Neither CTA may leave (or free tensor memory) while the other can still read its shared
+    // memory, arrive on its barriers or write its accumulator.
+    __syncwarp();
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace b2

@@ -160,6 +160,20 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
 int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, int* grid,
                   int* rows_per_launch);
 
+/* Tile shape of the tensor-memory GEMM (B2_ROUTE_TCGEN05).  B2_GEMM_SHAPE_AUTO picks per call
+ * by a cost model (waves x cost per tile); the others force one shape for every later call of
+ * the process, for tests and tuning.  The single-CTA shapes are rows of x by output columns per
+ * CTA; the PAIR shapes run on two SMs per tile (tcgen05 cta_group::2, weights through tensor
+ * memory): 256 output columns by 256 or 192 rows of x.  No counterpart in the reference, whose
+ * route table is fixed offline (dandan_ops/_dispatch.py). */
+#define B2_GEMM_SHAPE_AUTO 0
+#define B2_GEMM_SHAPE_128x128 1
+#define B2_GEMM_SHAPE_256x128 2
+#define B2_GEMM_SHAPE_256x192 3
+#define B2_GEMM_SHAPE_PAIR_256 4
+#define B2_GEMM_SHAPE_PAIR_192 5
+int b2_w4a16_set_gemm_shape(int shape);
+
 /* Number of kernels this library has launched from the calling process so far. */
 int64_t b2_w4a16_launch_count(void);
 

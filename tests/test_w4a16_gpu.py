@@ -299,6 +299,58 @@ def test_tcgen05_internal_weights_bit_exact(n, k):
         assert np.array_equal(got, want) and np.isfinite(got).all()
 
 
+@pytest.fixture
+def gemm_shape():
+    """Forces a tile shape of the tensor-memory GEMM for one test and restores the cost model."""
+    yield _native.set_gemm_shape
+    _native.set_gemm_shape("auto")
+
+
+@pytest.mark.parametrize("shape", ["128x128", "256x128", "256x192", "pair256", "pair192"])
+@pytest.mark.parametrize("m,n,k", [(65, 5, 8), (129, 127, 264), (300, 1000, 1024), (200, 12289, 1032), (1000, 1536, 4096)])
+def test_tcgen05_every_tile_shape(gemm_shape, shape, m, n, k):
+    """Each tile shape (single-CTA and two-SM pair kernels) on ragged sizes: tails in M, N and K."""
+    g = torch.Generator().manual_seed(m * 7 + n + k)
+    layer = ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.05).half().cuda())
+    x = torch.randn(m, k, generator=g).half().cuda()
+    bias = torch.randn(n, generator=g).half().cuda()
+    gemm_shape(shape)
+    y = _native.linear(x, layer._native_image(), n, k, route=_native.ROUTE_TCGEN05)
+    yb = _native.linear(x, layer._native_image(), n, k, route=_native.ROUTE_TCGEN05, bias=bias)
+    assert _native.status() == 0
+    expected = (x.double() @ layer.dequantize().half().double().t())
+    err = (y.double() - expected).abs()
+    assert bool((err <= ATOL + RTOL * expected.abs()).all())
+    assert torch.equal(yb, y + bias)                       # FP16 product first, FP16 bias add second
+    if m * n <= 400000:
+        assert_close_ref(y, oracle_y(x, layer))
+
+
+@pytest.mark.parametrize("shape", ["pair256", "pair192"])
+def test_pair_kernel_internal_weights_bit_exact(gemm_shape, shape):
+    """One-hot rows of x through the two-SM kernel (weights via tensor memory) return the FP16
+    weights exactly, and a strided output view is honoured."""
+    n, k = 300, 520
+    words, step, zero = cases.direct_state(n, k, n + 3 * k, lambda c: ops.pack_int4(c.cuda()))
+    layer = ops.QuantizedLinear(words, step.cuda(), zero.cuda(), in_features=k)
+    want = oracle.dequantize_fp16(layer.packed_weight.cpu().numpy(), layer.scales.cpu().numpy(),
+                                  layer.zeros.cpu().numpy(), k)
+    gemm_shape(shape)
+    eye = torch.eye(k, dtype=torch.float16, device="cuda")
+    y = _native.linear(eye, layer._native_image(), n, k, route=_native.ROUTE_TCGEN05)
+    got = y.t().contiguous().cpu().numpy()
+    assert np.array_equal(got, want) and np.isfinite(got).all()
+    assert _native.status() == 0
+
+
+def test_gemm_cost_model_picks_pair_kernels():
+    """Shapes on which the measured cost model prefers each family."""
+    assert _native.plan(512, 12288, 4096)["grid"] == 2 * 48 * 3         # pair, 192 rows of x per pair
+    assert _native.plan(512, 8192, 28672)["grid"] == 2 * 32 * 2         # pair, 256 rows of x per pair
+    assert _native.plan(256, 24576, 4096)["grid"] == 128                # single CTA, 256 x 192
+    assert _native.plan(100, 4096, 4096)["grid"] == 32                  # single CTA, 128 x 128
+
+
 def test_tcgen05_unaligned_falls_back_and_graph_replay():
     torch.manual_seed(9)
     layer = ops.QuantizedLinear.from_float(torch.randn(200, 129, dtype=torch.float16).cuda())
