@@ -290,9 +290,9 @@ int launch_gemm_one(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cu
     return after_launch("w4a16_gemm_kernel");
 }
 
-template <int MT>
-int launch_gemm_pair(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cudaStream_t s) {
-    auto kernel = b2::w4a16_gemm_pair_kernel<MT>;
+template <int MT, bool TMA_Y>
+int launch_gemm_pair(const CUtensorMap& map, const CUtensorMap& ymap, const b2::GemmArgs& a, dim3 grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_gemm_pair_kernel<MT, TMA_Y>;
     constexpr int smem = b2::pair_smem_bytes<MT>();
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -303,7 +303,7 @@ int launch_gemm_pair(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, c
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
-    kernel<<<grid, b2::kPairThreads, smem, s>>>(map, a);   // clusters of two along x (__cluster_dims__)
+    kernel<<<grid, b2::kPairThreads, smem, s>>>(map, ymap, a);   // clusters of two along x (__cluster_dims__)
     return after_launch("w4a16_gemm_pair_kernel");
 }
 
@@ -379,7 +379,19 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
     if (pair_mt) {
         const dim3 pgrid(2 * unsigned((d.n + 255) / 256), unsigned((m + pair_mt - 1) / pair_mt));
-        return pair_mt == 256 ? launch_gemm_pair<256>(map, a, pgrid, s) : launch_gemm_pair<192>(map, a, pgrid, s);
+        // y through TMA stores (32 columns x pair_mt/2 rows per warp) when its rows are 16-byte aligned
+        const bool tma_y = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0;
+        CUtensorMap ymap = map;
+        if (tma_y) {
+            const cuuint64_t ydims[2] = {cuuint64_t(d.n), cuuint64_t(m)};
+            const cuuint64_t ystrides[1] = {cuuint64_t(ldy) * 2};
+            const cuuint32_t ybox[2] = {32, cuuint32_t(pair_mt / 2)};
+            if (encode(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, y, ydims, ystrides, ybox, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled failed for y");
+            return pair_mt == 256 ? launch_gemm_pair<256, true>(map, ymap, a, pgrid, s) : launch_gemm_pair<192, true>(map, ymap, a, pgrid, s);
+        }
+        return pair_mt == 256 ? launch_gemm_pair<256, false>(map, ymap, a, pgrid, s) : launch_gemm_pair<192, false>(map, ymap, a, pgrid, s);
     }
     const int ma = shape.ma, bn = shape.bn;
     const dim3 grid((d.n + bn - 1) / bn, unsigned((m + 128 * ma - 1) / (128 * ma)));

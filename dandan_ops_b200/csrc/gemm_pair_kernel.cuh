@@ -108,13 +108,27 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-template <int MT>
+// Tile store shared -> global; rows and columns outside the tensor are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// TMA_Y: y is 16-byte aligned with a row stride that is a multiple of 16 bytes; the epilogue
+// then transposes through shared memory (the idle x ring) and stores each warp's 32 columns x
+// MT/2 rows with one TMA store.  Otherwise every thread stores its 2-byte results itself.
+template <int MT, bool TMA_Y>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, PairShape<MT>::CTAS)
-w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
+w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, const GemmArgs a) {
     constexpr int XS = PairShape<MT>::XS, WS = PairShape<MT>::WS, RS = PairShape<MT>::RS;
     constexpr int kXBytes = pair_x_bytes(MT);
     constexpr uint32_t kTmemCols = pair_tmem_cols<MT>();
     static_assert(WS <= XS && MT % 64 == 0, "one barrier ring serves both operand rings");
+    static_assert(kPairConverters * (MT / 2) * 64 <= XS * kXBytes, "the epilogue stages y in the x ring");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_base = smem;                                                // [XS][kXBytes]
@@ -263,6 +277,29 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs 
             const int n = n0 + r;
             const bool n_ok = n < a.n;
             const __half bias = (a.bias && n_ok) ? a.bias[n] : __float2half(0.0f);
+            if constexpr (TMA_Y) {
+                // [MT/2 rows of y][32 columns] FP16, 64-byte rows: the lanes of a warp write one row per store
+                uint8_t* stage = x_base + (warp - 2) * ((MT / 2) * 64);
+#pragma unroll 1
+                for (int cc = 0; cc < MT / 64; ++cc) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + lane_addr + half * (MT / 2) + cc * 32, v);
+                    __half* row = reinterpret_cast<__half*>(stage + cc * 32 * 64) + lane;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        __half hv = __float2half_rn(__uint_as_float(v[e]));
+                        if (a.bias) hv = __hadd(hv, bias);
+                        row[e * 32] = hv;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> TMA store
+                __syncwarp();
+                const int nw = n0 + quad * 32, mw = m0 + half * (MT / 2);
+                if (lane == 0 && nw < a.n && mw < a.m) {
+                    tma_store_2d(&ymap, smem_u32(stage), nw, mw);
+                    tma_store_wait_read();                                      // shared memory is released at exit
+                }
+            } else
 #pragma unroll 1
             for (int cc = 0; cc < MT / 64; ++cc) {
                 const int col = half * (MT / 2) + cc * 32;           // x rows col .. col+31 of the pair tile

@@ -115,10 +115,26 @@ __device__ __forceinline__ __half finish_output(float acc, const __half* bias, i
     const __half h = __float2half_rn(acc);
     return bias ? __hadd(h, bias[n]) : h;
 }
-// (lo*s, hi*s) rounded to an FP16 pair; each multiply is one IEEE FP32 rounding.
+// (lo*s, hi*s) rounded to an FP16 pair; each multiply is one IEEE FP32 rounding.  The two
+// multiplies go out as one packed instruction (mul.rn.f32x2): the same arithmetic in one issue
+// slot instead of two, and instruction issue is what bounds the dequantization.
+#ifndef B2_PACKED_FMUL
+#define B2_PACKED_FMUL 1
+#endif
 __device__ __forceinline__ uint32_t scale_pack(float lo, float hi, float s) {
+#if B2_PACKED_FMUL
+    uint32_t r;
+    asm("{\n\t.reg .b64 a, b, p;\n\t.reg .f32 x, y;\n\t"
+        "mov.b64 a, {%1, %2};\n\tmov.b64 b, {%3, %3};\n\t"
+        "mul.rn.f32x2 p, a, b;\n\t"
+        "mov.b64 {x, y}, p;\n\t"
+        "cvt.rn.f16x2.f32 %0, y, x;\n\t}"
+        : "=r"(r) : "f"(lo), "f"(hi), "f"(s));
+    return r;
+#else
     __half2 h = __floats2half2_rn(__fmul_rn(lo, s), __fmul_rn(hi, s));
     return *reinterpret_cast<uint32_t*>(&h);
+#endif
 }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
