@@ -25,7 +25,7 @@ _SIGNATURES = {
     "b2_w4a16_contract_version": (_int, []),
     "b2_w4a16_last_error": (ctypes.c_char_p, []),
     "b2_w4a16_launch_count": (_i64, []),
-    "b2_w4a16_set_gemm_shape": (_int, [_int]),
+    "b2_w4a16_set_gemm_shape": (_int, [_int, _int]),
     "b2_w4a16_native_bytes": (_i64, [_i64, _i64]),
     "b2_w4a16_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "b2_w4a16_unrepack": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
@@ -83,10 +83,14 @@ def launch_count():
     return int(load().b2_w4a16_launch_count())
 
 
-def set_gemm_shape(name="auto"):
-    """Force one tile shape of the tensor-memory GEMM for every later call (tests, tuning);
-    "auto" restores the per-call cost model."""
-    _check(load().b2_w4a16_set_gemm_shape(GEMM_SHAPES[name]))
+_need_cache = {}
+
+
+def set_gemm_shape(name="auto", k_splits=0):
+    """Force one tile shape of the tensor-memory GEMM (and, for the pair shapes, the number of
+    CTAs along K) for every later call (tests, tuning); "auto" / 0 restore the cost model."""
+    _check(load().b2_w4a16_set_gemm_shape(GEMM_SHAPES[name], k_splits))
+    _need_cache.clear()          # the workspace a problem needs depends on the shape
 
 
 def native_bytes(n, k):
@@ -191,9 +195,6 @@ def linear_static(x, image, n, k, out):
     return out
 
 
-_need_cache = {}
-
-
 def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
     """y[M,N] = x[M,K] @ W^T (+ FP16 bias [N]) on the current stream.  x must be CUDA FP16 with unit inner stride."""
     lib = _lib if _lib is not None else load()
@@ -205,7 +206,7 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=device)
     if m == 0:
         return y
-    key = (m if m <= STREAM_MAX_M else STREAM_MAX_M + 1, n, k, device.index)
+    key = (m, n, k, device.index)
     need = _need_cache.get(key)
     if need is None:
         need = _need_cache[key] = int(lib.b2_w4a16_workspace_bytes(m, n, k))

@@ -1,6 +1,7 @@
 // C ABI of the engine: argument checks, launch planning and kernel launches.
 // Declarations and the per-function reference citations are in include/b2_w4a16.h.
 #include <cuda_runtime.h>
+#include <algorithm>
 #include <atomic>
 #include <climits>
 #include <cstdio>
@@ -309,59 +310,76 @@ int launch_gemm_pair(const CUtensorMap& map, const CUtensorMap& ymap, const b2::
 
 // Tile shapes of the GEMM.  Single-CTA kernel: (rows of x) x (output columns) = 128 x 128,
 // 256 x 128 or 256 x 192 per CTA.  Pair kernel: 256 output columns x 256 rows of x per two SMs
-// (one CTA per SM), or x 192 rows with two CTAs per SM.  The cost of one tile per SM, measured on
+// (one CTA per SM), or x 192 rows with two CTAs per SM; it can also split K over up to 8 CTAs per
+// tile when a layer has fewer tiles than SM pairs.  The cost of one tile per SM, measured on
 // large layers, is about 10 : 12 : 15 for the single-CTA shapes and 9 / 6.75 for the pair shapes
-// (the pair kernel is ~10 % cheaper per multiply-add); the shape with the cheapest
-// waves x cost-per-tile wins.  With two co-resident CTAs a wave costs two units, a last wave that
-// fills at most half of the slots one.
+// (the pair kernel is ~10 % cheaper per multiply-add); prologue + epilogue cost about as much as
+// 10 of a tile's 64-column steps, a K-split adds the trip of the FP32 partial tiles through L2.
+// The candidate with the cheapest waves x cost-per-tile wins.  With two co-resident CTAs a wave
+// costs two units, a last wave that fills at most half of the slots one.
 struct GemmShape {
     int ma, bn;      // single-CTA kernel: accumulators of 128 x rows, output columns
     int pair_mt;     // pair kernel: rows of x per CTA pair (256 or 192), 0 = single-CTA kernel
-    int64_t ctas(int64_t m, int64_t n) const {
-        if (pair_mt) return 2 * ((n + 255) / 256) * ((m + pair_mt - 1) / pair_mt);
+    int splits;      // pair kernel: CTAs along K per tile
+    int64_t tiles(int64_t m, int64_t n) const {
+        if (pair_mt) return ((n + 255) / 256) * ((m + pair_mt - 1) / pair_mt);
         return ((n + bn - 1) / bn) * ((m + 128 * ma - 1) / (128 * ma));
     }
+    int64_t ctas(int64_t m, int64_t n) const { return tiles(m, n) * (pair_mt ? 2 * splits : 1); }
+    int64_t partial_bytes(int64_t m, int64_t n) const {
+        return splits > 1 ? tiles(m, n) * splits * 256 * pair_mt * int64_t(sizeof(float)) : 0;
+    }
 };
-constexpr GemmShape kGemmShapes[5] = {{1, 128, 0}, {2, 128, 0}, {2, 192, 0}, {0, 0, 256}, {0, 0, 192}};
+constexpr GemmShape kGemmShapes[5] = {{1, 128, 0, 1}, {2, 128, 0, 1}, {2, 192, 0, 1}, {0, 0, 256, 1}, {0, 0, 192, 1}};
+constexpr int kMaxSplits = 8;
 std::atomic<int> g_forced_shape{0};      // B2_GEMM_SHAPE_*, 0 = automatic
+std::atomic<int> g_forced_splits{0};     // K-splits of the pair kernel, 0 = automatic
 
-inline GemmShape gemm_shape(int64_t m, int64_t n, int sms) {
+// Largest split count a tile grid can use: at least four 256-column blocks per CTA and one ticket
+// per half tile in the workspace's ticket area (its last word is the status word).
+inline int max_splits(const GemmShape& g, int64_t m, int64_t n, int kb) {
+    if (g.pair_mt == 0 || 2 * g.tiles(m, n) > B2_W4A16_TICKET_BYTES / 4 - 1) return 1;
+    return std::max(1, std::min(kMaxSplits, kb / 4));
+}
+
+inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms) {
     const int forced = g_forced_shape.load(std::memory_order_relaxed);
-    if (forced >= 1 && forced <= 5) return kGemmShapes[forced - 1];
-    if (m <= 128) return kGemmShapes[0];
-    const int cost4[5] = {40, 48, 60, 36, 27};           // cost per tile and SM, times four
+    const int forced_splits = g_forced_splits.load(std::memory_order_relaxed);
     const int64_t pairs = sms >= 2 ? sms / 2 : 1;
+    auto units_of = [&](const GemmShape& g, int64_t items) -> int64_t {
+        if (g.pair_mt == 0) return (items + sms - 1) / sms;
+        if (g.pair_mt == 256) return (items + pairs - 1) / pairs;
+        const int64_t rem = items % (2 * pairs);
+        return 2 * (items / (2 * pairs)) + (rem == 0 ? 0 : rem <= pairs ? 1 : 2);
+    };
+    const int cost4[5] = {40, 48, 60, 36, 27};           // cost per tile and SM, times four
     GemmShape best = kGemmShapes[1];
     int64_t best_cost = INT64_MAX;
     for (int i = 0; i < 5; ++i) {
-        const GemmShape& g = kGemmShapes[i];
-        int64_t units;
-        if (g.pair_mt == 0) {
-            units = (g.ctas(m, n) + sms - 1) / sms;
-        } else {
-            const int64_t tiles = g.ctas(m, n) / 2;
-            if (g.pair_mt == 256) {
-                units = (tiles + pairs - 1) / pairs;
-            } else {
-                const int64_t rem = tiles % (2 * pairs);
-                units = 2 * (tiles / (2 * pairs)) + (rem == 0 ? 0 : rem <= pairs ? 1 : 2);
-            }
+        if (forced ? i != forced - 1 : (m <= 128 && i != 0)) continue;
+        GemmShape g = kGemmShapes[i];
+        const int smax = max_splits(g, m, n, kb);
+        for (int sp = 1; sp <= smax; ++sp) {
+            if (forced_splits && sp != std::min(forced_splits, smax)) continue;
+            g.splits = sp;
+            const int64_t steps = int64_t((kb + sp - 1) / sp) * 4 + 10 + (sp > 1 ? 4 + 2 * sp : 0);
+            const int64_t c = units_of(g, g.tiles(m, n) * sp) * cost4[i] * steps;
+            if (c < best_cost) { best_cost = c; best = g; }
         }
-        const int64_t c = units * cost4[i];
-        if (c < best_cost) { best_cost = c; best = g; }
     }
     return best;
 }
 
 int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
-             const b2::Dims& d, void* workspace, cudaStream_t s, int sms, const void* bias) {
+             const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s, int sms, const void* bias) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return fail(B2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
     if (workspace == nullptr) return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(m)};
     const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
-    const GemmShape shape = gemm_shape(m, d.n, sms);
+    GemmShape shape = gemm_shape(m, d.n, d.kb, sms);
+    if (B2_W4A16_TICKET_BYTES + shape.partial_bytes(m, d.n) > workspace_bytes) shape.splits = 1;   // no room: one CTA per tile
     const int pair_mt = shape.pair_mt;
     const cuuint32_t box[2] = {cuuint32_t(b2::kGemmBK), pair_mt ? cuuint32_t(pair_mt / 2) : 128u};
     const cuuint32_t elem[2] = {1, 1};
@@ -376,9 +394,12 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.bias = static_cast<const __half*>(bias);
     a.ldy = ldy;
     a.m = int(m); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
+    a.tickets = static_cast<unsigned*>(workspace);
+    a.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + B2_W4A16_TICKET_BYTES);
+    a.splits = shape.splits;
     const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
     if (pair_mt) {
-        const dim3 pgrid(2 * unsigned((d.n + 255) / 256), unsigned((m + pair_mt - 1) / pair_mt));
+        const dim3 pgrid(2 * unsigned((d.n + 255) / 256), unsigned((m + pair_mt - 1) / pair_mt), unsigned(shape.splits));
         // y through TMA stores (32 columns x pair_mt/2 rows per warp) when its rows are 16-byte aligned
         const bool tma_y = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0;
         CUtensorMap ymap = map;
@@ -410,10 +431,12 @@ const char* b2_w4a16_last_error(void) { return g_error.c_str(); }
 
 int64_t b2_w4a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int b2_w4a16_set_gemm_shape(int shape) {
+int b2_w4a16_set_gemm_shape(int shape, int k_splits) {
     if (shape < B2_GEMM_SHAPE_AUTO || shape > B2_GEMM_SHAPE_PAIR_192)
         return fail(B2_ERR_ARGUMENT, "unknown GEMM tile shape");
+    if (k_splits < 0 || k_splits > kMaxSplits) return fail(B2_ERR_ARGUMENT, "k_splits must be 0 (automatic) to 8");
     g_forced_shape.store(shape, std::memory_order_relaxed);
+    g_forced_splits.store(k_splits, std::memory_order_relaxed);
     return B2_OK;
 }
 
@@ -484,9 +507,9 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
     const b2::Dims d = b2::make_dims(n, k);
     const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
     if (m > B2_STREAM_MAX_M && d.k % 8 == 0) {     // assuming an aligned x, as execution_info cannot see the pointer
-        const GemmShape shape = gemm_shape(m, d.n, dev.sm_count > 0 ? dev.sm_count : 148);
+        const GemmShape shape = gemm_shape(m, d.n, d.kb, dev.sm_count > 0 ? dev.sm_count : 148);
         if (route) *route = B2_ROUTE_TCGEN05;
-        if (k_splits) *k_splits = 1;
+        if (k_splits) *k_splits = shape.splits;
         if (grid) *grid = int(shape.ctas(m, d.n));
         if (rows_per_launch) *rows_per_launch = int(m);
         return B2_OK;
@@ -519,7 +542,11 @@ int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (check_dims(n, k) != B2_OK || m < 0) return B2_W4A16_TICKET_BYTES;
     DeviceInfo dev;
     if (device_info(dev) != B2_OK) dev.sm_count = 148;
-    return stream_workspace_bytes(m > 0 ? m : 1, b2::make_dims(n, k), dev.sm_count);
+    const b2::Dims d = b2::make_dims(n, k);
+    int64_t need = stream_workspace_bytes(m > 0 ? m : 1, d, dev.sm_count);
+    if (m > B2_STREAM_MAX_M)      // room for the partial tiles of a K-split tensor-memory GEMM
+        need = std::max(need, B2_W4A16_TICKET_BYTES + gemm_shape(m, d.n, d.kb, dev.sm_count > 0 ? dev.sm_count : 148).partial_bytes(m, d.n));
+    return need;
 }
 
 int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
@@ -560,7 +587,7 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
         if (workspace_bytes < B2_W4A16_TICKET_BYTES)
             return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
-        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, static_cast<cudaStream_t>(stream), dev.sm_count, bias);
+        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), dev.sm_count, bias);
     }
     return fail(B2_ERR_UNSUPPORTED, "unknown route");
 }

@@ -61,6 +61,12 @@ struct GemmArgs {
     int64_t ldy;
     int m, n, k;
     int n16, kb;
+    // K-splitting (pair kernel only): blockIdx.z works on its share of the 256-column blocks and
+    // the FP32 partial tiles meet in `partial`; the last CTA to arrive at a tile's ticket adds
+    // them in split order (deterministic) and writes y.  splits == 1: neither pointer is used.
+    float* partial;
+    unsigned* tickets;
+    int splits;
 };
 
 // ---- tcgen05 / TMA helpers ----------------------------------------------------------------

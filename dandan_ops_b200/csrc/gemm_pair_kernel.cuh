@@ -32,6 +32,13 @@
 //   w_full[s]              leader only: one arrival per converter warp of both CTAs
 //   x_free[s], w_free[s]   both CTAs: tcgen05.commit (multicast) after the MMAs that read stage s
 //   acc_full               both CTAs: tcgen05.commit after the last MMA
+//   epi_written, epi_last  local, K-splitting only: the CTA's partial tile is in global memory /
+//                          thread 64 has drawn the tile's ticket
+//
+// K-splitting (layers with fewer tiles than SM pairs and a long K): blockIdx.z takes a share of
+// the 256-column blocks, every CTA stores its FP32 accumulator to the workspace, and the CTA that
+// draws the last ticket of its half tile adds the partial tiles in split order - the same
+// deterministic scheme as the streaming kernel's - and writes y.
 #pragma once
 #include "gemm_kernel.cuh"
 
@@ -137,10 +144,11 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
     // FULL[s % XS] (leader): the x bytes of both CTAs and every converter warp's weights of step s
     // are in place.  DONE[s % XS] (both CTAs): the MMAs of step s have completed.
     constexpr int RAW_FULL = 0, RAW_FREE = RAW_FULL + RS, FULL = RAW_FREE + RS, DONE = FULL + XS,
-                  ACC_FULL = DONE + XS, NBARS = ACC_FULL + 1;
-    static_assert(NBARS * 8 + 8 <= 512, "barrier area");
+                  ACC_FULL = DONE + XS, EPI_WRITTEN = ACC_FULL + 1, EPI_LAST = EPI_WRITTEN + 1, NBARS = EPI_LAST + 1;
+    static_assert(NBARS * 8 + 12 <= 512, "barrier area");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + i * 8; };
 
@@ -150,9 +158,15 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
     const int tile_n = blockIdx.x >> 1, tile_m = blockIdx.y;
     const int m0 = tile_m * MT;                                            // first x row of the pair
     const int n0 = tile_n * (2 * kPairRows) + int(rank) * kPairRows;       // first weight row of this CTA
-    const int ksteps = (a.k + kGemmBK - 1) / kGemmBK;
+    // this CTA's share of K: 256-column blocks [kb0, kb1), 64-column steps s0 .. s0 + ksteps - 1
+    const int split = blockIdx.z;
+    const int kb0 = int(int64_t(split) * a.kb / a.splits), kb1 = int(int64_t(split + 1) * a.kb / a.splits);
+    const int s0 = kb0 * 4;
+    const int ksteps = min((a.k + kGemmBK - 1) / kGemmBK, kb1 * 4) - s0;
 
     if (threadIdx.x == 0) {
+        mbar_init(bar(EPI_WRITTEN), kPairConverters);
+        mbar_init(bar(EPI_LAST), 1);
         for (int i = 0; i < RS; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_FREE + i), kPairConverters); }
         for (int i = 0; i < XS; ++i) { mbar_init(bar(FULL + i), 1 + 2 * kPairConverters); mbar_init(bar(DONE + i), 1); }
         mbar_init(bar(ACC_FULL), 1);
@@ -194,7 +208,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
                     if (kb >= RS && !wait(RAW_FREE + r, ((kb / RS) - 1) & 1)) break;
                     if (raw_bytes) {
                         mbar_expect_tx(bar(RAW_FULL + r), raw_bytes);
-                        bulk_copy_g2s(smem_u32(raw_base + r * kPairRawBytes), src + kb * stride, raw_bytes, bar(RAW_FULL + r));
+                        bulk_copy_g2s(smem_u32(raw_base + r * kPairRawBytes), src + (kb0 + kb) * stride, raw_bytes, bar(RAW_FULL + r));
                     } else {
                         mbar_arrive(bar(RAW_FULL + r));       // no weight rows here: columns beyond N, masked in the epilogue
                     }
@@ -202,7 +216,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
                 const int st = s % XS;
                 if (s >= XS && !wait(DONE + st, ((s / XS) - 1) & 1)) break;
                 if (leader) mbar_expect_tx(bar(FULL + st), 2 * kXBytes);
-                tma_load_2d_pair(smem_u32(x_base + st * kXBytes), &xmap, s * kGemmBK, m0 + int(rank) * (MT / 2), full_leader + st * 8);
+                tma_load_2d_pair(smem_u32(x_base + st * kXBytes), &xmap, (s0 + s) * kGemmBK, m0 + int(rank) * (MT / 2), full_leader + st * 8);
             }
         }
     } else if (warp == 1) {
@@ -277,13 +291,76 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
             const int n = n0 + r;
             const bool n_ok = n < a.n;
             const __half bias = (a.bias && n_ok) ? a.bias[n] : __float2half(0.0f);
-            if constexpr (TMA_Y) {
+            const bool split_k = a.splits > 1;
+            // Partial tiles of this half tile: [split][32-column chunk][4 columns][128 weight rows] FP32 x 4,
+            // so that the 32 lanes of a warp store and load 512 contiguous bytes per instruction.
+            constexpr int kTileVec = kPairRows * MT / 4;             // 16-byte vectors per half tile and split
+            const int64_t half_tile = (int64_t(tile_m) * (gridDim.x >> 1) + tile_n) * 2 + rank;
+            uint4* part0 = reinterpret_cast<uint4*>(a.partial) + half_tile * a.splits * int64_t(kTileVec)
+                           + (half * (MT / 64)) * (8 * kPairRows) + r;
+            bool write_y = true;
+            if (split_k) {
+                uint4* mine = part0 + int64_t(split) * kTileVec;
+#pragma unroll 1
+                for (int cc = 0; cc < MT / 64; ++cc) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + lane_addr + half * (MT / 2) + cc * 32, v);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        mine[(cc * 8 + q) * kPairRows] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(EPI_WRITTEN));
+                if (threadIdx.x == 64) {
+                    if (wait(EPI_WRITTEN, 0)) {
+                        __threadfence();
+                        const unsigned t = atomicAdd(a.tickets + half_tile, 1u);
+                        const bool last = t == unsigned(a.splits - 1);
+                        if (last) a.tickets[half_tile] = 0;          // every split has arrived: ready for the next call
+                        __threadfence();
+                        *last_flag = last ? 1u : 0u;
+                    } else {
+                        *last_flag = 0u;
+                    }
+                    mbar_arrive(bar(EPI_LAST));
+                }
+                write_y = wait(EPI_LAST, 0) && *last_flag != 0;
+            }
+            // accumulator chunk cc of this thread: from tensor memory, or the partial tiles added in split order
+            auto load_chunk = [&](int cc, uint32_t (&v)[32]) {
+                if (!split_k) {
+                    tmem_ld32(tmem_base + lane_addr + half * (MT / 2) + cc * 32, v);
+                    return;
+                }
+                const uint4* src = part0 + cc * (8 * kPairRows);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {                          // split 0
+                    const uint4 f = __ldcg(src + q * kPairRows);
+                    v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+                }
+                for (int sp = 1; sp < a.splits; ++sp) {                 // then 1, 2, ... in this order
+                    src += kTileVec;
+                    uint4 f[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) f[q] = __ldcg(src + q * kPairRows);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + __uint_as_float(f[q].x));
+                        v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + __uint_as_float(f[q].y));
+                        v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + __uint_as_float(f[q].z));
+                        v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + __uint_as_float(f[q].w));
+                    }
+                }
+            };
+            if (!write_y) {
+                // another CTA adds the partial tiles
+            } else if constexpr (TMA_Y) {
                 // [MT/2 rows of y][32 columns] FP16, 64-byte rows: the lanes of a warp write one row per store
                 uint8_t* stage = x_base + (warp - 2) * ((MT / 2) * 64);
 #pragma unroll 1
                 for (int cc = 0; cc < MT / 64; ++cc) {
                     uint32_t v[32];
-                    tmem_ld32(tmem_base + lane_addr + half * (MT / 2) + cc * 32, v);
+                    load_chunk(cc, v);
                     __half* row = reinterpret_cast<__half*>(stage + cc * 32 * 64) + lane;
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
@@ -299,20 +376,21 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
                     tma_store_2d(&ymap, smem_u32(stage), nw, mw);
                     tma_store_wait_read();                                      // shared memory is released at exit
                 }
-            } else
+            } else {
 #pragma unroll 1
-            for (int cc = 0; cc < MT / 64; ++cc) {
-                const int col = half * (MT / 2) + cc * 32;           // x rows col .. col+31 of the pair tile
-                uint32_t v[32];
-                tmem_ld32(tmem_base + lane_addr + col, v);
-                if (n_ok) {
-                    __half* dst = a.y + int64_t(m0 + col) * a.ldy + n;
+                for (int cc = 0; cc < MT / 64; ++cc) {
+                    const int col = half * (MT / 2) + cc * 32;           // x rows col .. col+31 of the pair tile
+                    uint32_t v[32];
+                    load_chunk(cc, v);
+                    if (n_ok) {
+                        __half* dst = a.y + int64_t(m0 + col) * a.ldy + n;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        if (m0 + col + e < a.m) {
-                            __half hv = __float2half_rn(__uint_as_float(v[e]));
-                            if (a.bias) hv = __hadd(hv, bias);
-                            dst[int64_t(e) * a.ldy] = hv;
+                        for (int e = 0; e < 32; ++e) {
+                            if (m0 + col + e < a.m) {
+                                __half hv = __float2half_rn(__uint_as_float(v[e]));
+                                if (a.bias) hv = __hadd(hv, bias);
+                                dst[int64_t(e) * a.ldy] = hv;
+                            }
                         }
                     }
                 }

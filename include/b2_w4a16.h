@@ -172,7 +172,12 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
 #define B2_GEMM_SHAPE_256x192 3
 #define B2_GEMM_SHAPE_PAIR_256 4
 #define B2_GEMM_SHAPE_PAIR_192 5
-int b2_w4a16_set_gemm_shape(int shape);
+/* k_splits: CTAs along K per tile of the PAIR shapes, 1..8, or 0 = by the cost model (K is split
+ * when a layer has fewer tiles than SM pairs; the FP32 partial tiles meet in the workspace and
+ * are added in split order, so results do not depend on timing).  A split the problem or the
+ * workspace cannot take (fewer than four 256-column blocks per CTA, too many tiles for the ticket
+ * area, workspace smaller than b2_w4a16_workspace_bytes()) is reduced. */
+int b2_w4a16_set_gemm_shape(int shape, int k_splits);
 
 /* Number of kernels this library has launched from the calling process so far. */
 int64_t b2_w4a16_launch_count(void);

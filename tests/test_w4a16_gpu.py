@@ -343,12 +343,40 @@ def test_pair_kernel_internal_weights_bit_exact(gemm_shape, shape):
     assert _native.status() == 0
 
 
+@pytest.mark.parametrize("shape,splits", [("pair256", 2), ("pair256", 5), ("pair192", 3), ("pair192", 8)])
+@pytest.mark.parametrize("m,n,k", [(129, 127, 4104), (300, 1000, 8192), (512, 1536, 5120)])
+def test_pair_kernel_k_split(gemm_shape, shape, splits, m, n, k):
+    """K split over several CTAs per tile: FP32 partial tiles through the workspace, added in split
+    order.  Same tolerance as one CTA per tile, identical bits from call to call, tickets left zero."""
+    g = torch.Generator().manual_seed(m + n + k + splits)
+    layer = ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.05).half().cuda())
+    x = torch.randn(m, k, generator=g).half().cuda()
+    bias = torch.randn(n, generator=g).half().cuda()
+    image = layer._native_image()
+    gemm_shape(shape, splits)
+    assert _native.plan(m, n, k)["k_splits"] == min(splits, (k + 255) // 256 // 4)
+    y = _native.linear(x, image, n, k, route=_native.ROUTE_TCGEN05)
+    again = _native.linear(x, image, n, k, route=_native.ROUTE_TCGEN05)
+    yb = _native.linear(x, image, n, k, route=_native.ROUTE_TCGEN05, bias=bias)
+    assert _native.status() == 0
+    assert torch.equal(y, again) and torch.equal(yb, y + bias)
+    expected = (x.double() @ layer.dequantize().half().double().t())
+    assert bool(((y.double() - expected).abs() <= ATOL + RTOL * expected.abs()).all())
+    gemm_shape(shape, 1)
+    one = _native.linear(x, image, n, k, route=_native.ROUTE_TCGEN05)
+    torch.testing.assert_close(y, one, atol=ATOL, rtol=RTOL)
+    ws = list(_native._workspaces.values())[0]
+    assert int(ws[:_native.TICKET_BYTES - 4].view(torch.int32).abs().sum()) == 0
+
+
 def test_gemm_cost_model_picks_pair_kernels():
     """Shapes on which the measured cost model prefers each family."""
     assert _native.plan(512, 12288, 4096)["grid"] == 2 * 48 * 3         # pair, 192 rows of x per pair
     assert _native.plan(512, 8192, 28672)["grid"] == 2 * 32 * 2         # pair, 256 rows of x per pair
     assert _native.plan(256, 24576, 4096)["grid"] == 128                # single CTA, 256 x 192
     assert _native.plan(100, 4096, 4096)["grid"] == 32                  # single CTA, 128 x 128
+    split = _native.plan(256, 4096, 28672)                              # 16 tiles, 112 blocks of K: four CTAs per tile
+    assert split["k_splits"] == 4 and split["grid"] == 2 * 16 * 4
 
 
 def test_tcgen05_unaligned_falls_back_and_graph_replay():
