@@ -111,6 +111,13 @@ def repack(packed, scales, zeros, k):
     return image
 
 
+def image_from_host(host_bytes, device):
+    """A native image read back from storage (uint8 CPU tensor) -> uint8 tensor on `device`."""
+    if host_bytes.dtype != torch.uint8 or host_bytes.ndim != 1:
+        raise ValueError("a native image is a flat uint8 tensor")
+    return host_bytes.to(device)
+
+
 def unrepack(image, n, k):
     lib = load()
     dev = image.device

@@ -312,11 +312,10 @@ int launch_gemm_pair(const CUtensorMap& map, const CUtensorMap& ymap, const b2::
 // 256 x 128 or 256 x 192 per CTA.  Pair kernel: 256 output columns x 256 rows of x per two SMs
 // (one CTA per SM), or x 192 rows with two CTAs per SM; it can also split K over up to 8 CTAs per
 // tile when a layer has fewer tiles than SM pairs.  The cost of one tile per SM, measured on
-// large layers, is about 10 : 12 : 15 for the single-CTA shapes and 9 / 6.75 for the pair shapes
-// (the pair kernel is ~10 % cheaper per multiply-add); prologue + epilogue cost about as much as
-// 10 of a tile's 64-column steps, a K-split adds the trip of the FP32 partial tiles through L2.
-// The candidate with the cheapest waves x cost-per-tile wins.  With two co-resident CTAs a wave
-// costs two units, a last wave that fills at most half of the slots one.
+// large layers, is about 10 : 12 : 15 for the single-CTA shapes and 9 / 5.25 for the pair shapes;
+// prologue + epilogue cost about as much as 10 of a tile's 64-column steps, a K-split adds the
+// trip of the FP32 partial tiles through L2.  The candidate with the cheapest
+// waves x cost-per-tile wins.
 struct GemmShape {
     int ma, bn;      // single-CTA kernel: accumulators of 128 x rows, output columns
     int pair_mt;     // pair kernel: rows of x per CTA pair (256 or 192), 0 = single-CTA kernel
@@ -346,13 +345,17 @@ inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms) {
     const int forced = g_forced_shape.load(std::memory_order_relaxed);
     const int forced_splits = g_forced_splits.load(std::memory_order_relaxed);
     const int64_t pairs = sms >= 2 ? sms / 2 : 1;
-    auto units_of = [&](const GemmShape& g, int64_t items) -> int64_t {
-        if (g.pair_mt == 0) return (items + sms - 1) / sms;
-        if (g.pair_mt == 256) return (items + pairs - 1) / pairs;
+    // waves x cost per tile and SM (times four).  Two co-resident 192-row tiles cost 21 each; one
+    // that has its SM pair to itself takes 34, nearly as long as a 256-row tile (36): the
+    // converters' latency, not the MMA, sets the pace of a lone CTA.
+    const int cost4[5] = {40, 48, 60, 36, 21};
+    constexpr int kLone192 = 34;
+    auto wave_cost = [&](int i, const GemmShape& g, int64_t items) -> int64_t {
+        if (g.pair_mt == 0) return (items + sms - 1) / sms * cost4[i];
+        if (g.pair_mt == 256) return (items + pairs - 1) / pairs * cost4[i];
         const int64_t rem = items % (2 * pairs);
-        return 2 * (items / (2 * pairs)) + (rem == 0 ? 0 : rem <= pairs ? 1 : 2);
+        return 2 * (items / (2 * pairs)) * cost4[i] + (rem == 0 ? 0 : rem <= pairs ? kLone192 : 2 * cost4[i]);
     };
-    const int cost4[5] = {40, 48, 60, 36, 27};           // cost per tile and SM, times four
     GemmShape best = kGemmShapes[1];
     int64_t best_cost = INT64_MAX;
     for (int i = 0; i < 5; ++i) {
@@ -363,7 +366,7 @@ inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms) {
             if (forced_splits && sp != std::min(forced_splits, smax)) continue;
             g.splits = sp;
             const int64_t steps = int64_t((kb + sp - 1) / sp) * 4 + 10 + (sp > 1 ? 4 + 2 * sp : 0);
-            const int64_t c = units_of(g, g.tiles(m, n) * sp) * cost4[i] * steps;
+            const int64_t c = wave_cost(i, g, g.tiles(m, n) * sp) * steps;
             if (c < best_cost) { best_cost = c; best = g; }
         }
     }

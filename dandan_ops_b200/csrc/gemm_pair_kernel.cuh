@@ -106,12 +106,15 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                  "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
                  ::"r"(bar) : "memory");
 }
-// 16 registers -> 16 columns of this thread's tensor-memory lane.
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+// 32 registers -> 32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
                  ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                   "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                   "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
@@ -168,7 +171,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
         mbar_init(bar(EPI_WRITTEN), kPairConverters);
         mbar_init(bar(EPI_LAST), 1);
         for (int i = 0; i < RS; ++i) { mbar_init(bar(RAW_FULL + i), 1); mbar_init(bar(RAW_FREE + i), kPairConverters); }
-        for (int i = 0; i < XS; ++i) { mbar_init(bar(FULL + i), 1 + 2 * kPairConverters); mbar_init(bar(DONE + i), 1); }
+        for (int i = 0; i < XS; ++i) { mbar_init(bar(FULL + i), 1 + kPairConverters); mbar_init(bar(DONE + i), 1); }   // x bytes + 4 converter warps of each CTA
         mbar_init(bar(ACC_FULL), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -250,26 +253,30 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
     } else {
         // ------------------------------ converters ---------------------------------------
         const int quad = warp & 3;                      // tensor-memory lane quadrant this warp may access
-        const int half = (warp - 2) >> 2;               // which 32 of the step's 64 columns
+        const int half = (warp - 2) >> 2;               // converts the steps with s % 2 == half; epilogue: column half
         const int r = quad * 32 + lane;                 // weight row of this CTA = tensor-memory lane
         const int blk = r >> 4, rr = r & 15, g = rr & 7, hi8 = rr >> 3;
         const uint32_t full_leader = map_to_cta(bar(FULL), 0);
         const uint32_t lane_addr = uint32_t(quad * 32) << 16;
         bool ok = true;
-        for (int s = 0; s < ksteps && ok; ++s) {
+        int waited_kb = -1;
+        // The two warps of a lane quadrant alternate steps: one 32-column tensor-memory store per
+        // step and quadrant, and two steps of time for a thread's 64 weights.
+        for (int s = half; s < ksteps && ok; s += 2) {
             const int kb = s >> 2, t = s & 3, rs = kb % RS;
-            if (t == 0) ok = wait(RAW_FULL + rs, (kb / RS) & 1);
+            if (kb != waited_kb) { ok = wait(RAW_FULL + rs, (kb / RS) & 1); waited_kb = kb; }
             if (!ok) break;
             const uint8_t* nb = raw_base + rs * kPairRawBytes + blk * kBlockBytes;
             const int lane_idx = 4 * g + t;
-            const uint4 code = *reinterpret_cast<const uint4*>(nb + (2 * hi8 + half) * 512 + lane_idx * 16);
+            const uint4 code0 = *reinterpret_cast<const uint4*>(nb + (2 * hi8) * 512 + lane_idx * 16);
+            const uint4 code1 = *reinterpret_cast<const uint4*>(nb + (2 * hi8 + 1) * 512 + lane_idx * 16);
             const float step = *reinterpret_cast<const float*>(nb + kStepOffset + (lane_idx * 2 + hi8) * 4);
             const float z = float((nb[kZeroOffset + lane_idx] >> (4 * hi8)) & 15);
             const float c_even = -(1024.0f + z), c_odd = -(64.0f + z);
-            const uint32_t words[4] = {code.x, code.y, code.z, code.w};
-            uint32_t o[16];
+            const uint32_t words[8] = {code0.x, code0.y, code0.z, code0.w, code1.x, code1.y, code1.z, code1.w};
+            uint32_t o[32];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < 8; ++i) {
                 const uint4 q = dequant_word(words[i], c_even, c_odd, step);
                 o[4 * i] = q.x; o[4 * i + 1] = q.y; o[4 * i + 2] = q.z; o[4 * i + 3] = q.w;
             }
@@ -277,12 +284,13 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
             if (s >= WS) ok = wait(DONE + (s - WS) % XS, ((s - WS) / XS) & 1);
             if (!ok) break;
             tcgen05_fence_after();
-            tmem_st16(tmem_w + lane_addr + (s % WS) * kPairWCols + half * 16, o);
+            tmem_st32(tmem_w + lane_addr + (s % WS) * kPairWCols, o);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive_cluster(full_leader + (s % XS) * 8);
-                if (t == 3 || s == ksteps - 1) mbar_arrive(bar(RAW_FREE + rs));
+                // last step of this warp in the raw stage (its later steps belong to the next block)
+                if (((s + 2) >> 2) != kb || s + 2 >= ksteps) mbar_arrive(bar(RAW_FREE + rs));
             }
         }
         // ------------------------------ epilogue -----------------------------------------

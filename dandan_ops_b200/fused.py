@@ -1,0 +1,94 @@
+"""Projection sets that share an input, run as one N-concatenated launch.
+
+The reference keeps q/k/v and gate/up as separate layers and refuses to combine its INT4
+path with the engine's projection fusion (dandan_ops/integrations/myvllm.py:96-97), while its
+benchmarks time the fused shapes (`qkv_fused`, `gate_up_fused`,
+benchmarks/bench_qwen3_gemm.py:50-57).  Output column n of a W4A16 linear depends only on row n
+of the quantized state, so stacking the rows of several layers gives exactly the layers'
+columns side by side: one weight stream, one launch, no change to any value of the state.
+"""
+import torch
+from torch import nn
+
+from .quantized_linear import QuantizedLinear
+
+
+def concat_layers(layers, backend=None):
+    """One QuantizedLinear whose rows are the rows of `layers` in order (same in_features,
+    group size and device).  A missing bias counts as zeros when any layer has one."""
+    layers = list(layers)
+    if not layers or not all(isinstance(l, QuantizedLinear) for l in layers):
+        raise TypeError("concat_layers takes a non-empty sequence of QuantizedLinear layers")
+    first = layers[0]
+    for layer in layers[1:]:
+        if layer.in_features != first.in_features or layer.group_size != first.group_size:
+            raise ValueError("fused projections must share in_features and group_size")
+        if layer.packed_weight.device != first.packed_weight.device:
+            raise ValueError("fused projections must share a device")
+    bias = None
+    if any(l.bias is not None for l in layers):
+        dtype = next(l.bias.dtype for l in layers if l.bias is not None)
+        bias = torch.cat([l.bias.to(dtype) if l.bias is not None
+                          else torch.zeros(l.out_features, dtype=dtype, device=first.packed_weight.device)
+                          for l in layers])
+    return QuantizedLinear(torch.cat([l.packed_weight for l in layers]), torch.cat([l.scales for l in layers]),
+                           torch.cat([l.zeros for l in layers]), in_features=first.in_features,
+                           group_size=first.group_size, bias=bias, backend=backend or first.backend)
+
+
+class FusedProjections(nn.Module):
+    """`forward(x)` returns one output per original layer (views of one [M, sum N_i] result).
+
+    `unfuse()` gives the original layers back, state bit-identical, e.g. to save a checkpoint
+    in the per-projection format."""
+
+    def __init__(self, layers, names=None):
+        super().__init__()
+        layers = list(layers)
+        self.op = concat_layers(layers)
+        self.split_sizes = [l.out_features for l in layers]
+        self.names = list(names) if names is not None else [str(i) for i in range(len(layers))]
+        if len(self.names) != len(layers):
+            raise ValueError("one name per fused layer")
+        self._had_bias = [l.bias is not None for l in layers]
+        self.in_features, self.out_features = self.op.in_features, self.op.out_features
+        self.eval()
+
+    @property
+    def storage_bytes(self):
+        return self.op.storage_bytes
+
+    def execution_info(self, x):
+        return self.op.execution_info(x)
+
+    def forward(self, x):
+        y = self.op(x)
+        return y.split(self.split_sizes, dim=1)
+
+    def unfuse(self):
+        out, row = [], 0
+        for rows, had_bias in zip(self.split_sizes, self._had_bias):
+            sl = slice(row, row + rows)
+            out.append(QuantizedLinear(self.op.packed_weight[sl].clone(), self.op.scales[sl].clone(),
+                                       self.op.zeros[sl].clone(), in_features=self.in_features,
+                                       group_size=self.op.group_size,
+                                       bias=self.op.bias[sl].clone() if had_bias else None,
+                                       backend=self.op.backend))
+            row += rows
+        return out
+
+
+def fuse_named_projections(parent, names, fused_name=None):
+    """Replace the child modules `names` of `parent` (QuantizedLinear layers or adapters that
+    hold one in `.op`) by one FusedProjections child called `fused_name` (default: the names
+    joined by '_').  The caller changes its forward to use the fused child's tuple output.
+    Returns the new module."""
+    children = [getattr(parent, n) for n in names]
+    layers = [c if isinstance(c, QuantizedLinear) else getattr(c, "op", None) for c in children]
+    if not all(isinstance(l, QuantizedLinear) for l in layers):
+        raise TypeError("every fused child must be a QuantizedLinear or hold one in .op")
+    fused = FusedProjections(layers, names)
+    for n in names:
+        delattr(parent, n)
+    setattr(parent, fused_name or "_".join(names), fused)
+    return fused

@@ -215,6 +215,16 @@ class QuantizedLinear(torch.nn.Module):
             self._image_key = key
         return self._image
 
+    def attach_native_image(self, image):
+        """Use a prebuilt device image of THIS layer's state (e.g. from `checkpoint.ImageCache`)
+        instead of repacking.  The image is dropped again if the state tensors change."""
+        if image.dtype != torch.uint8 or image.device != self.packed_weight.device or \
+                image.numel() != _native.native_bytes(self.out_features, self.in_features):
+            raise ValueError("not a native image of this layer")
+        self._image = image
+        self._image_key = (self.packed_weight.data_ptr(), self.scales.data_ptr(), self.zeros.data_ptr(),
+                           self.packed_weight._version, self.scales._version, self.zeros._version)
+
     def _bias_fp16(self):
         """FP16 copy of the bias for the fused epilogue (derived, rebuilt when the bias changes)."""
         if self.bias is None:

@@ -1,0 +1,127 @@
+"""Fused projection sets (one N-concatenated launch) and checkpoint tooling.
+
+CPU tests cover the state handling; the GPU tests compare with the separate layers and with a
+fresh repack."""
+import numpy as np
+import pytest
+import torch
+
+import dandan_ops_b200 as ops
+from dandan_ops_b200 import _native, checkpoint
+from dandan_ops_b200.fused import FusedProjections, concat_layers, fuse_named_projections
+
+
+def _layer(n, k, seed, bias=False, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    w = (torch.randn(n, k, generator=g) * 0.03).half().to(device)
+    b = torch.randn(n, generator=g).half().to(device) if bias else None
+    return ops.QuantizedLinear.from_float(w, b)
+
+
+def test_concat_state_is_the_rows_side_by_side():
+    q, k, v = _layer(48, 200, 1), _layer(16, 200, 2), _layer(17, 200, 3)
+    fused = FusedProjections([q, k, v], names=["q", "k", "v"])
+    assert fused.out_features == 81 and fused.split_sizes == [48, 16, 17]
+    assert torch.equal(fused.op.packed_weight[48:64], k.packed_weight)
+    assert torch.equal(fused.op.scales[64:], v.scales) and torch.equal(fused.op.zeros[:48], q.zeros)
+    back = fused.unfuse()
+    for a, b in zip(back, (q, k, v)):
+        assert a.bias is None
+        for key in ("packed_weight", "scales", "zeros"):
+            assert torch.equal(getattr(a, key), getattr(b, key))
+        assert a.get_extra_state() == b.get_extra_state()
+
+
+def test_concat_bias_and_errors():
+    a, b = _layer(8, 64, 1, bias=True), _layer(8, 64, 2)
+    both = concat_layers([a, b])
+    assert torch.equal(both.bias[:8], a.bias) and torch.count_nonzero(both.bias[8:]) == 0
+    assert [l.bias is None for l in FusedProjections([a, b]).unfuse()] == [False, True]
+    with pytest.raises(ValueError, match="in_features"):
+        concat_layers([a, _layer(8, 128, 3)])
+    with pytest.raises(TypeError):
+        concat_layers([])
+    with pytest.raises(ValueError, match="one name"):
+        FusedProjections([a, b], names=["only"])
+
+
+def test_fuse_named_children():
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = _layer(32, 64, 1), _layer(32, 64, 2), _layer(64, 32, 3)
+    block = Block()
+    fused = fuse_named_projections(block, ["gate_proj", "up_proj"])
+    assert block.gate_proj_up_proj is fused and not hasattr(block, "gate_proj") and hasattr(block, "down_proj")
+    assert fused.names == ["gate_proj", "up_proj"] and fused.out_features == 64
+
+
+def test_checkpoint_round_trip_is_unchanged():
+    layers = {"model.layers.0.q.": _layer(24, 130, 1, bias=True), "model.layers.0.o.": _layer(40, 64, 2), "": _layer(8, 64, 3)}
+    state = checkpoint.export_int4_layers(layers)
+    state["model.norm.weight"] = torch.ones(4)
+    assert checkpoint.int4_prefixes(state) == sorted(layers)
+    loaded = checkpoint.load_int4_layers(state, device="cpu")
+    again = checkpoint.export_int4_layers(loaded)
+    assert set(again) == set(state) - {"model.norm.weight"}
+    for key, value in again.items():
+        if isinstance(value, torch.Tensor):
+            assert value.dtype == state[key].dtype and torch.equal(value, state[key])
+        else:
+            assert value == state[key] and value["format_version"] == 2
+    broken = dict(state)
+    broken["model.layers.0.o._extra_state"] = dict(broken["model.layers.0.o._extra_state"], format_version=3)
+    with pytest.raises((ValueError, RuntimeError)):
+        checkpoint.load_int4_layers(broken, device="cpu")
+
+
+def test_image_file_format_and_digest(tmp_path):
+    a, b = _layer(24, 130, 1), _layer(24, 130, 2)
+    da = checkpoint.state_digest(a.packed_weight, a.scales, a.zeros, a.in_features)
+    assert da == checkpoint.state_digest(a.packed_weight.clone(), a.scales.clone(), a.zeros.clone(), 130)
+    assert da != checkpoint.state_digest(b.packed_weight, b.scales, b.zeros, b.in_features)
+    assert da != checkpoint.state_digest(a.packed_weight, a.scales, a.zeros, 129) and len(da) == 64
+    image = np.arange(4672, dtype=np.uint8)
+    path = tmp_path / "x.b2img"
+    checkpoint.write_image_file(str(path), image, 24, 130)
+    assert path.stat().st_size == 64 + 4672 and path.read_bytes()[:8] == b"B2W4IMG1"
+    assert np.array_equal(checkpoint.read_image_file(str(path), 24, 130, 4672), image)
+    assert checkpoint.read_image_file(str(path), 24, 131, 4672) is None          # another layer's shape
+    assert checkpoint.read_image_file(str(path), 24, 130, 4673) is None
+    path.write_bytes(path.read_bytes()[:100])                                       # truncated file
+    assert checkpoint.read_image_file(str(path), 24, 130, 4672) is None
+    assert checkpoint.read_image_file(str(tmp_path / "missing"), 24, 130, 4672) is None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [1, 8, 100, 300])
+def test_fused_projections_match_separate_layers(m):
+    q, k, v = (_layer(n, 1024, s, bias=(s == 2), device="cuda") for n, s in ((2048, 1), (1000, 2), (24, 3)))
+    fused = FusedProjections([q, k, v])
+    x = torch.randn(m, 1024, generator=torch.Generator().manual_seed(m)).half().cuda()
+    outs = fused(x)
+    assert [o.shape[1] for o in outs] == [2048, 1000, 24]
+    for got, layer in zip(outs, (q, k, v)):
+        want = layer(x)
+        torch.testing.assert_close(got, want, atol=2e-3, rtol=2e-3)
+        if m <= 16:          # whole-K tile route: the sum order does not depend on N, bits agree
+            assert torch.equal(got, want)
+    assert _native.status() == 0
+    assert fused.execution_info(x)["kernel_plan"]["route"] == q.execution_info(x)["kernel_plan"]["route"]
+
+
+@pytest.mark.gpu
+def test_image_cache_hit_equals_repack(tmp_path):
+    cache = checkpoint.ImageCache(tmp_path)
+    layer = _layer(300, 1032, 5, device="cuda")
+    fresh = layer._native_image().clone()
+    assert cache.attach(layer) is False and cache.misses == 1           # built and stored
+    twin = ops.QuantizedLinear(layer.packed_weight.clone(), layer.scales.clone(), layer.zeros.clone(), in_features=1032)
+    assert cache.attach(twin) is True and cache.hits == 1
+    assert torch.equal(twin._native_image(), fresh)
+    x = torch.randn(5, 1032).half().cuda()
+    assert torch.equal(twin(x), layer(x))
+    with pytest.raises(ValueError, match="native image"):
+        twin.attach_native_image(fresh[:-16])
+    twin.scales.mul_(2)                                                  # state changed: the attached image is dropped
+    assert not torch.equal(twin._native_image(), fresh)

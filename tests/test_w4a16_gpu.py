@@ -372,7 +372,7 @@ def test_pair_kernel_k_split(gemm_shape, shape, splits, m, n, k):
 def test_gemm_cost_model_picks_pair_kernels():
     """Shapes on which the measured cost model prefers each family."""
     assert _native.plan(512, 12288, 4096)["grid"] == 2 * 48 * 3         # pair, 192 rows of x per pair
-    assert _native.plan(512, 8192, 28672)["grid"] == 2 * 32 * 2         # pair, 256 rows of x per pair
+    assert _native.plan(2048, 4096, 4096)["grid"] == 2 * 16 * 8         # pair, 256 rows of x per pair
     assert _native.plan(256, 24576, 4096)["grid"] == 128                # single CTA, 256 x 192
     assert _native.plan(100, 4096, 4096)["grid"] == 32                  # single CTA, 128 x 128
     split = _native.plan(256, 4096, 28672)                              # 16 tiles, 112 blocks of K: four CTAs per tile
