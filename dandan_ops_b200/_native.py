@@ -38,6 +38,8 @@ _SIGNATURES = {
     "b2_w4a16_linear_static": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "b2_w4a16_linear_route": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_linear_bias": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
+    "b2_w4a16_linear_silu_mul": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_silu_mul_pairs": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b2_w4a16_plan": (_int, [_i64, _i64, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int),
                              ctypes.POINTER(_int), ctypes.POINTER(_int)]),
 }
@@ -227,3 +229,37 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
     if rc != OK:
         _check(rc)
     return y
+
+
+def linear_silu_mul(x, image, n, k, bias=None, out=None):
+    """Fused gate/up projection on a pair-ordered image: [M, K] -> [M, N/2] (see include/b2_w4a16.h).
+    M <= 64 runs the epilogue inside the decode kernels; larger batches run the GEMM and then the
+    elementwise pair kernel."""
+    lib = load()
+    m = x.shape[0]
+    device = x.device
+    y = out if out is not None else torch.empty((m, n // 2), dtype=torch.float16, device=device)
+    if m == 0:
+        return y
+    with torch.cuda.device(device):
+        stream = _stream()
+        if m > STREAM_MAX_M:
+            full = linear(x, image, n, k, bias=bias)
+            _check(lib.b2_w4a16_silu_mul_pairs(full.data_ptr(), full.stride(0), y.data_ptr(), y.stride(0), m, n, stream))
+            return y
+        ws = workspace(device, int(lib.b2_w4a16_workspace_bytes(m, n, k)))
+        _check(lib.b2_w4a16_linear_silu_mul(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
+                                            bias.data_ptr() if bias is not None else None, y.data_ptr(),
+                                            y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream))
+    return y
+
+
+def silu_mul_pairs(y_pairs):
+    """Elementwise SiLU(gate) * up on a pair-ordered [M, N] FP16 tensor -> [M, N/2]."""
+    lib = load()
+    m, n = y_pairs.shape
+    out = torch.empty((m, n // 2), dtype=torch.float16, device=y_pairs.device)
+    with torch.cuda.device(y_pairs.device):
+        _check(lib.b2_w4a16_silu_mul_pairs(y_pairs.data_ptr(), y_pairs.stride(0), out.data_ptr(), out.stride(0),
+                                           m, n, _stream()))
+    return out

@@ -167,8 +167,9 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 }
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
-             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias) {
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0) {
     b2::TileArgs a;
+    a.act = act;
     a.x = static_cast<const __half*>(x);
     a.native = static_cast<const uint8_t*>(native);
     a.y = static_cast<__half*>(y);
@@ -185,7 +186,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
                const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s,
-               const DeviceInfo& dev, const void* bias) {
+               const DeviceInfo& dev, const void* bias, int act = 0) {
     const int64_t ticket_bytes = B2_W4A16_TICKET_BYTES;
     const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
     for (int64_t m0 = 0; m0 < m; m0 += B2_STREAM_MAX_M) {
@@ -196,10 +197,11 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         b2::StreamArgs a;
         a.x = static_cast<const __half*>(x) + m0 * ldx;
         a.native = static_cast<const uint8_t*>(native);
-        a.y = static_cast<__half*>(y) + m0 * ldy;
+        a.y = static_cast<__half*>(y) + m0 * ldy;      // (act: at most one chunk, see linear_impl)
         a.ticket = static_cast<unsigned*>(workspace);
         a.status = a.ticket + (B2_W4A16_TICKET_BYTES / 4 - 1);
         a.bias = static_cast<const __half*>(bias);
+        a.act = act;
         a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ticket_bytes);
         a.ldx = ldx; a.ldy = ldy;
         a.m = int(rows); a.n = d.n; a.k = d.k;
@@ -552,16 +554,35 @@ int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     return need;
 }
 
-int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
-                         int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
-                         int64_t workspace_bytes, void* stream, int route) {
+}  // extern "C"
+
+namespace {
+
+// Elementwise fallback of the fused gate/up epilogue for batches the decode kernels do not take:
+// in[m][16 j + g] is the gate and in[m][16 j + 8 + g] the up value of output column 8 j + g.
+__global__ void silu_mul_pairs_kernel(const __half* in, int64_t ld_in, __half* out, int64_t ld_out, int m, int half_n) {
+    const int64_t total = int64_t(m) * half_n;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+        const int row = int(i / half_n), col = int(i % half_n);
+        const __half* src = in + row * ld_in + (col >> 3) * 16 + (col & 7);
+        out[row * ld_out + col] = b2::silu_mul(src[0], src[8]);
+    }
+}
+
+// act = 1: rows g / g+8 of every 16-row tile are a gate/up pair and y gets n/2 columns.
+int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                int64_t workspace_bytes, void* stream, int route, int act) {
     const void* bias = bias_fp16;
     if (bias && reinterpret_cast<uintptr_t>(bias) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
     if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
     if (int rc = check_dims(n, k)) return rc;
     if (m == 0) return B2_OK;
     if (!x || !native || !y) return fail(B2_ERR_ARGUMENT, "null pointer");
-    if (ldx < k || ldy < n) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+    if (ldx < k || ldy < (act ? n / 2 : n)) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+    if (act && (n % 16 != 0 || m > B2_STREAM_MAX_M))
+        return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue needs N % 16 == 0 and M <= 64 "
+                                        "(larger batches: b2_w4a16_linear, then b2_w4a16_silu_mul_pairs)");
     if (m > INT_MAX - 128 || m * k > INT_MAX || m * n > INT_MAX)
         return fail(B2_ERR_RANGE, "W4A16 dimensions exceed the kernel index range");
     if (reinterpret_cast<uintptr_t>(native) % 16) return fail(B2_ERR_ARGUMENT, "native image must be 16-byte aligned");
@@ -576,15 +597,16 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
     if (route == B2_ROUTE_AUTO)
         route = tile_applicable(m, d) ? B2_ROUTE_TILE
               : (m > B2_STREAM_MAX_M && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
+    if (act && route == B2_ROUTE_TCGEN05) return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue runs in the decode kernels only");
     if (route == B2_ROUTE_TILE) {
         if (!tile_applicable(m, d))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
-        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias);
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act);
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
-                          static_cast<cudaStream_t>(stream), dev, bias);
+                          static_cast<cudaStream_t>(stream), dev, bias, act);
     if (route == B2_ROUTE_TCGEN05) {
         if (!gemm_applicable(x, ldx, d))
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
@@ -593,6 +615,36 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
         return run_gemm(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), dev.sm_count, bias);
     }
     return fail(B2_ERR_UNSUPPORTED, "unknown route");
+}
+
+}  // namespace
+
+extern "C" {
+
+int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                         int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                         int64_t workspace_bytes, void* stream, int route) {
+    return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, route, 0);
+}
+
+int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                             int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+    return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 1);
+}
+
+int b2_w4a16_silu_mul_pairs(const void* y_pairs, int64_t ld_in, void* out, int64_t ld_out, int64_t m, int64_t n,
+                            void* stream) {
+    if (m < 0 || n <= 0 || n % 16 != 0) return fail(B2_ERR_ARGUMENT, "m >= 0 and n a positive multiple of 16 expected");
+    if (m == 0) return B2_OK;
+    if (!y_pairs || !out) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (ld_in < n || ld_out < n / 2) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+    if (m > INT_MAX || m * n > INT_MAX) return fail(B2_ERR_RANGE, "W4A16 dimensions exceed the kernel index range");
+    const int64_t total = m * (n / 2);
+    const unsigned blocks = unsigned(std::min<int64_t>((total + 255) / 256, 148 * 8));
+    silu_mul_pairs_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(y_pairs), ld_in, static_cast<__half*>(out), ld_out, int(m), int(n / 2));
+    return after_launch("silu_mul_pairs_kernel");
 }
 
 int b2_w4a16_linear_route(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy,

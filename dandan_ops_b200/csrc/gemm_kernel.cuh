@@ -119,15 +119,13 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 }
 
 // Eight weights of one native word -> eight FP16 values in column order (16 bytes).
-__device__ __forceinline__ uint4 dequant_word(uint32_t w, float c_even, float c_odd, float s) {
-    float d[8];
-    add_mixed(and_or(w, 0x000F000Fu, 0x64006400u), c_even, d[0], d[1]);
-    fma_mixed_16th(and_or(w, 0x00F000F0u, 0x64006400u), c_odd, d[2], d[3]);
+// s2 = twice(step), c_even = -(1024 + zero), c_odd = -(64 + zero).
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, float c_even, float c_odd, uint64_t s2) {
     const uint32_t u = w >> 8;
-    add_mixed(and_or(u, 0x000F000Fu, 0x64006400u), c_even, d[4], d[5]);
-    fma_mixed_16th(and_or(u, 0x00F000F0u, 0x64006400u), c_odd, d[6], d[7]);
-    return make_uint4(scale_pack(d[0], d[1], s), scale_pack(d[2], d[3], s),
-                      scale_pack(d[4], d[5], s), scale_pack(d[6], d[7], s));
+    return make_uint4(dequant_pair_even(and_or(w, 0x000F000Fu, 0x64006400u), c_even, s2),
+                      dequant_pair_odd(and_or(w, 0x00F000F0u, 0x64006400u), c_odd, s2),
+                      dequant_pair_even(and_or(u, 0x000F000Fu, 0x64006400u), c_even, s2),
+                      dequant_pair_odd(and_or(u, 0x00F000F0u, 0x64006400u), c_odd, s2));
 }
 
 // MA = accumulators of 128 rows of x each (1 or 2).  VEC: y rows may be written with
@@ -259,7 +257,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int chunk = 4 * h + i;
-                *reinterpret_cast<uint4*>(brow + ((chunk ^ (r & 7)) << 4)) = dequant_word(words[i], c_even, c_odd, step);
+                *reinterpret_cast<uint4*>(brow + ((chunk ^ (r & 7)) << 4)) = dequant_word(words[i], c_even, c_odd, twice(step));
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> MMA (async proxy)
             __syncwarp();

@@ -273,11 +273,12 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
             const float step = *reinterpret_cast<const float*>(nb + kStepOffset + (lane_idx * 2 + hi8) * 4);
             const float z = float((nb[kZeroOffset + lane_idx] >> (4 * hi8)) & 15);
             const float c_even = -(1024.0f + z), c_odd = -(64.0f + z);
+            const uint64_t step2 = twice(step);
             const uint32_t words[8] = {code0.x, code0.y, code0.z, code0.w, code1.x, code1.y, code1.z, code1.w};
             uint32_t o[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 q = dequant_word(words[i], c_even, c_odd, step);
+                const uint4 q = dequant_word(words[i], c_even, c_odd, step2);
                 o[4 * i] = q.x; o[4 * i + 1] = q.y; o[4 * i + 2] = q.z; o[4 * i + 3] = q.w;
             }
             // the conversion happens in registers before the wait for the free tensor-memory stage

@@ -76,6 +76,8 @@ struct StreamArgs {
     int m, n, k;
     int n16, kb;            // row tiles, column blocks
     int groups;             // row groups = ceil(n16 / W)
+    int act;                // 0: y = x W^T (+bias); 1: rows g / g+8 of every 16-row tile are a gate/up pair,
+                            //    y[:, 8*tile + g] = silu_mul(gate, up), y has n/2 columns
     int max_parts;          // partial slots per row tile
     int steps;              // groups * kb (below 2^20 for every layer the index checks admit)
 };
@@ -115,25 +117,64 @@ __device__ __forceinline__ __half finish_output(float acc, const __half* bias, i
     const __half h = __float2half_rn(acc);
     return bias ? __hadd(h, bias[n]) : h;
 }
-// (lo*s, hi*s) rounded to an FP16 pair; each multiply is one IEEE FP32 rounding.  The two
-// multiplies go out as one packed instruction (mul.rn.f32x2): the same arithmetic in one issue
-// slot instead of two, and instruction issue is what bounds the dequantization.
+// SiLU(gate) * up on FP16 values with the reference's rounding order: the activation is rounded
+// to FP16 before the multiplication (dandan_ops/csrc/elementwise.cu:70-73,
+// `torch.nn.functional.silu(gate) * up` on the CPU route).
+__device__ __forceinline__ __half silu_mul(__half gate, __half up) {
+    const float v = __half2float(gate);
+    const __half act = __float2half_rn(v / (1.0f + expf(-v)));
+    return __float2half_rn(__half2float(act) * __half2float(up));
+}
+// Exact dequantization of one FP16 pair, `1024 + code` (even nibbles) or `1024 + 16 * code` (odd
+// nibbles), to fp16_rn(fp32(code - zero) * step): a mixed-precision add (or fma by 1/16) gives
+// the exact FP32 integer, one FP32 multiply applies the step (one IEEE rounding), cvt rounds the
+// pair to FP16.  The two multiplies go out as one packed mul.rn.f32x2 - same rounding per element,
+// one issue slot instead of two, and instruction issue is what bounds the dequantization; the
+// whole pair is one asm block so that the register pairs of the packed operands need no moves,
+// and the step arrives already duplicated in a 64-bit register (`twice()`, once per group).
 #ifndef B2_PACKED_FMUL
 #define B2_PACKED_FMUL 1
 #endif
-__device__ __forceinline__ uint32_t scale_pack(float lo, float hi, float s) {
+__device__ __forceinline__ uint64_t twice(float s) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(s));
+    return r;
+}
+__device__ __forceinline__ float low_of(uint64_t s2) { return __uint_as_float(uint32_t(s2)); }
+// c = -(1024 + zero)
+__device__ __forceinline__ uint32_t dequant_pair_even(uint32_t h2, float c, uint64_t s2) {
 #if B2_PACKED_FMUL
     uint32_t r;
-    asm("{\n\t.reg .b64 a, b, p;\n\t.reg .f32 x, y;\n\t"
-        "mov.b64 a, {%1, %2};\n\tmov.b64 b, {%3, %3};\n\t"
-        "mul.rn.f32x2 p, a, b;\n\t"
-        "mov.b64 {x, y}, p;\n\t"
+    asm("{\n\t.reg .b16 l, h;\n\t.reg .f32 x, y;\n\t.reg .b64 a;\n\t"
+        "mov.b32 {l, h}, %1;\n\t"
+        "add.rn.f32.f16 x, l, %2;\n\tadd.rn.f32.f16 y, h, %2;\n\t"
+        "mov.b64 a, {x, y};\n\tmul.rn.f32x2 a, a, %3;\n\tmov.b64 {x, y}, a;\n\t"
         "cvt.rn.f16x2.f32 %0, y, x;\n\t}"
-        : "=r"(r) : "f"(lo), "f"(hi), "f"(s));
+        : "=r"(r) : "r"(h2), "f"(c), "l"(s2));
     return r;
 #else
-    __half2 h = __floats2half2_rn(__fmul_rn(lo, s), __fmul_rn(hi, s));
-    return *reinterpret_cast<uint32_t*>(&h);
+    float lo, hi;
+    add_mixed(h2, c, lo, hi);
+    __half2 p = __floats2half2_rn(__fmul_rn(lo, low_of(s2)), __fmul_rn(hi, low_of(s2)));
+    return *reinterpret_cast<uint32_t*>(&p);
+#endif
+}
+// c = -(64 + zero): (1024 + 16 * code) / 16 + c, exact (the product is an integer below 2^11)
+__device__ __forceinline__ uint32_t dequant_pair_odd(uint32_t h2, float c, uint64_t s2) {
+#if B2_PACKED_FMUL
+    uint32_t r;
+    asm("{\n\t.reg .b16 l, h, q;\n\t.reg .f32 x, y;\n\t.reg .b64 a;\n\t"
+        "mov.b32 {l, h}, %1;\n\tmov.b16 q, 0x2C00;\n\t"
+        "fma.rn.f32.f16 x, l, q, %2;\n\tfma.rn.f32.f16 y, h, q, %2;\n\t"
+        "mov.b64 a, {x, y};\n\tmul.rn.f32x2 a, a, %3;\n\tmov.b64 {x, y}, a;\n\t"
+        "cvt.rn.f16x2.f32 %0, y, x;\n\t}"
+        : "=r"(r) : "r"(h2), "f"(c), "l"(s2));
+    return r;
+#else
+    float lo, hi;
+    fma_mixed_16th(h2, c, lo, hi);
+    __half2 p = __floats2half2_rn(__fmul_rn(lo, low_of(s2)), __fmul_rn(hi, low_of(s2)));
+    return *reinterpret_cast<uint32_t*>(&p);
 #endif
 }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -328,7 +369,7 @@ w4a16_stream_kernel(const StreamArgs a) {
                 const float zg = float(zero & 15u), zh = float(zero >> 4);
                 const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);   // even nibbles: (1024+q) - (1024+z)
                 const float eg = -(64.0f + zg), eh = -(64.0f + zh);       // odd nibbles: (1024+16q)/16 - (64+z)
-                const float sg = step.x, sh = step.y;
+                const uint64_t sg = twice(step.x), sh = twice(step.y);
                 const uint8_t* xchunk = xs + ((kb - xorigin) * 4 + t) * kChunk + g * 144;
 #pragma unroll
                 for (int wi = 0; wi < 8; ++wi) {
@@ -341,13 +382,10 @@ w4a16_stream_kernel(const StreamArgs a) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
-                        float d[8];
-                        add_mixed(and_or(ua, 0x000F000Fu, 0x64006400u), cg, d[0], d[1]);
-                        add_mixed(and_or(ub, 0x000F000Fu, 0x64006400u), ch, d[2], d[3]);
-                        fma_mixed_16th(and_or(ua, 0x00F000F0u, 0x64006400u), eg, d[4], d[5]);
-                        fma_mixed_16th(and_or(ub, 0x00F000F0u, 0x64006400u), eh, d[6], d[7]);
-                        const uint32_t w[4] = {scale_pack(d[0], d[1], sg), scale_pack(d[2], d[3], sh),
-                                               scale_pack(d[4], d[5], sg), scale_pack(d[6], d[7], sh)};
+                        const uint32_t w[4] = {dequant_pair_even(and_or(ua, 0x000F000Fu, 0x64006400u), cg, sg),
+                                               dequant_pair_even(and_or(ub, 0x000F000Fu, 0x64006400u), ch, sh),
+                                               dequant_pair_odd(and_or(ua, 0x00F000F0u, 0x64006400u), eg, sg),
+                                               dequant_pair_odd(and_or(ub, 0x00F000F0u, 0x64006400u), eh, sh)};
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt)
                             mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
@@ -399,10 +437,20 @@ w4a16_stream_kernel(const StreamArgs a) {
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     const int m0 = mt * 8 + 2 * t;
+                    if (a.act) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int m = m0 + (c & 1), n = n0 + 8 * (c >> 1);
-                        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(acc[mt][c], a.bias, n);
+                        for (int c = 0; c < 2; ++c) {           // this thread holds the gate (row g) and up (row g+8) sums
+                            const int m = m0 + c;
+                            if (m < a.m && n0 + 8 < a.n)
+                                a.y[int64_t(m) * a.ldy + nt * 8 + g] = silu_mul(finish_output(acc[mt][c], a.bias, n0),
+                                                                               finish_output(acc[mt][c + 2], a.bias, n0 + 8));
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int m = m0 + (c & 1), n = n0 + 8 * (c >> 1);
+                            if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(acc[mt][c], a.bias, n);
+                        }
                     }
                 }
             }

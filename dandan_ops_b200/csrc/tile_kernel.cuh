@@ -31,6 +31,7 @@ struct TileArgs {
     int m, n, k;
     int n16, kb;
     int warps;              // warps per CTA = min(16, 2*kb)
+    int act;                // as StreamArgs::act
 };
 
 __host__ __device__ constexpr int tile_smem_bytes(int kb, int mt, int warps) {
@@ -101,7 +102,7 @@ w4a16_tile_kernel(const TileArgs a) {
         const float zg = float(zero & 15u), zh = float(zero >> 4);
         const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);
         const float eg = -(64.0f + zg), eh = -(64.0f + zh);
-        const float sg = step.x, sh = step.y;
+        const uint64_t sg = twice(step.x), sh = twice(step.y);
         const uint8_t* xchunk = xs + (b * 4 + t) * kChunk + g * 144 + h * 64;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -113,13 +114,10 @@ w4a16_tile_kernel(const TileArgs a) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
-                float d[8];
-                add_mixed(and_or(ua, 0x000F000Fu, 0x64006400u), cg, d[0], d[1]);
-                add_mixed(and_or(ub, 0x000F000Fu, 0x64006400u), ch, d[2], d[3]);
-                fma_mixed_16th(and_or(ua, 0x00F000F0u, 0x64006400u), eg, d[4], d[5]);
-                fma_mixed_16th(and_or(ub, 0x00F000F0u, 0x64006400u), eh, d[6], d[7]);
-                const uint32_t w[4] = {scale_pack(d[0], d[1], sg), scale_pack(d[2], d[3], sh),
-                                       scale_pack(d[4], d[5], sg), scale_pack(d[6], d[7], sh)};
+const uint32_t w[4] = {dequant_pair_even(and_or(ua, 0x000F000Fu, 0x64006400u), cg, sg),
+                                       dequant_pair_even(and_or(ub, 0x000F000Fu, 0x64006400u), ch, sh),
+                                       dequant_pair_odd(and_or(ua, 0x00F000F0u, 0x64006400u), eg, sg),
+                                       dequant_pair_odd(and_or(ub, 0x00F000F0u, 0x64006400u), eh, sh)};
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
                     mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
@@ -132,6 +130,23 @@ w4a16_tile_kernel(const TileArgs a) {
         red[(warp * MT + mt) * 32 + lane] = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
     __syncthreads();
     // thread e adds element e of every warp's tile in warp order and stores one output
+    if (a.act) {
+        // gate (row rg) and up (row rg + 8) of one output: elements c and c + 2 of the same fragment
+        for (int e = threadIdx.x; e < MT * 64; e += blockDim.x) {
+            const int mt = e >> 6, rl = (e >> 1) & 31, c = e & 1;
+            float gate = 0.0f, up = 0.0f;
+            for (int w = 0; w < a.warps; ++w) {
+                const float* f = reinterpret_cast<const float*>(red) + ((w * MT + mt) * 32 + rl) * 4;
+                gate += f[c];
+                up += f[c + 2];
+            }
+            const int rg = rl >> 2, rt = rl & 3;
+            const int m = mt * 8 + 2 * rt + c, n = nt * 16 + rg;
+            if (m < a.m && n + 8 < a.n)
+                a.y[int64_t(m) * a.ldy + nt * 8 + rg] = silu_mul(finish_output(gate, a.bias, n), finish_output(up, a.bias, n + 8));
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < MT * 128; e += blockDim.x) {
         const int mt = e >> 7, rl = (e >> 2) & 31, c = e & 3;
         float sum = 0.0f;

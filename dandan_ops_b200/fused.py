@@ -10,6 +10,7 @@ columns side by side: one weight stream, one launch, no change to any value of t
 import torch
 from torch import nn
 
+from . import _native
 from .quantized_linear import QuantizedLinear
 
 
@@ -76,6 +77,66 @@ class FusedProjections(nn.Module):
                                        backend=self.op.backend))
             row += rows
         return out
+
+
+def pair_order(rows, device=None):
+    """Row permutation of a [gate; up] stack of 2 x `rows` rows into pair order: every 16-row tile
+    holds 8 gate rows followed by the 8 up rows of the same output columns."""
+    if rows % 8:
+        raise ValueError("the fused gate/up epilogue needs a multiple of 8 output columns")
+    j = torch.arange(rows, device=device).view(-1, 8)
+    return torch.cat([j, j + rows], dim=1).reshape(-1)
+
+
+class GateUpSilu(nn.Module):
+    """SiLU(gate(x)) * up(x) of a gated MLP as ONE launch.
+
+    The reference runs the fused `gate_up` projection and then a separate `silu_and_mul` kernel
+    (dandan_ops/elementwise.py:168-173).  Here the rows of the two layers are interleaved in
+    groups of eight so that a thread of the decode kernels ends up with the gate and the up sum
+    of the same output column, and the activation is applied before anything is written: the
+    [M, 2I] intermediate never exists for M <= 64.  Rounding follows the reference: both sums to
+    FP16 (plus FP16 bias), SiLU rounded to FP16, product rounded to FP16."""
+
+    def __init__(self, gate, up):
+        super().__init__()
+        if gate.out_features != up.out_features:
+            raise ValueError("gate and up projections must have the same number of rows")
+        stacked = concat_layers([gate, up])
+        order = pair_order(gate.out_features, stacked.packed_weight.device)
+        self.op = QuantizedLinear(stacked.packed_weight[order], stacked.scales[order], stacked.zeros[order],
+                                  in_features=stacked.in_features, group_size=stacked.group_size,
+                                  bias=None if stacked.bias is None else stacked.bias[order], backend=stacked.backend)
+        self.in_features, self.out_features = gate.in_features, gate.out_features
+        self._had_bias = (gate.bias is not None, up.bias is not None)
+        self.eval()
+
+    @property
+    def storage_bytes(self):
+        return self.op.storage_bytes
+
+    def forward(self, x):
+        if not isinstance(x, torch.Tensor) or x.ndim != 2 or x.shape[1] != self.in_features:
+            raise ValueError("x must have shape [M, in_features]")
+        if x.dtype != torch.float16 or not x.is_cuda or x.device != self.op.packed_weight.device:
+            raise ValueError("the fused gate/up projection requires CUDA FP16 input on the layer's device")
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        return _native.linear_silu_mul(x, self.op._native_image(), self.op.out_features, self.in_features,
+                                       bias=self.op._bias_fp16())
+
+    def unfuse(self):
+        """The original (gate, up) layers, state bit-identical."""
+        inverse = torch.empty_like(pair_order(self.out_features, self.op.packed_weight.device))
+        inverse[pair_order(self.out_features, inverse.device)] = torch.arange(2 * self.out_features, device=inverse.device)
+        out = []
+        for part, had_bias in zip((0, 1), self._had_bias):
+            rows = inverse[part * self.out_features:(part + 1) * self.out_features]
+            out.append(QuantizedLinear(self.op.packed_weight[rows].clone(), self.op.scales[rows].clone(),
+                                       self.op.zeros[rows].clone(), in_features=self.in_features,
+                                       group_size=self.op.group_size,
+                                       bias=self.op.bias[rows].clone() if had_bias else None, backend=self.op.backend))
+        return tuple(out)
 
 
 def fuse_named_projections(parent, names, fused_name=None):

@@ -154,6 +154,23 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
                          int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                          int64_t workspace_bytes, void* stream, int route);
 
+/* Fused gate/up projection of a gated MLP: y[M, N/2] = SiLU(g) * u with g, u = the FP16 outputs
+ * (bias included) of the gate and up rows, rounded as the reference's separate launch does
+ * (`silu_and_mul`: SiLU rounded to FP16 before the multiplication, dandan_ops/elementwise.py:168-173,
+ * dandan_ops/csrc/elementwise.cu:70-73).  The image must be built from rows in PAIR ORDER: every
+ * 16-row tile holds 8 gate rows followed by the 8 up rows of the same output columns
+ * (N % 16 == 0), and `bias_fp16` follows the same order.  The product and the activation never
+ * leave the SM: the decode kernels hold a gate/up pair in one thread.  M <= B2_STREAM_MAX_M;
+ * larger batches call b2_w4a16_linear on the same image and then b2_w4a16_silu_mul_pairs. */
+int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                             int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+
+/* out[M, N/2] = SiLU(in[m][16j+g]) * in[m][16j+8+g] for out column 8j+g: the elementwise form of
+ * the epilogue above, for outputs of b2_w4a16_linear on a pair-ordered image. */
+int b2_w4a16_silu_mul_pairs(const void* y_pairs, int64_t ld_in, void* out, int64_t ld_out, int64_t m, int64_t n,
+                            void* stream);
+
 /* Which kernel family B2_ROUTE_AUTO picks for this problem (a B2_ROUTE_* value) and,
  * through the optional out-parameters, the launch plan: K-splits, grid size, rows of x
  * handled per launch.  Pure host arithmetic; used by execution_info(). */

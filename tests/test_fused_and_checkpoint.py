@@ -8,7 +8,7 @@ import torch
 
 import dandan_ops_b200 as ops
 from dandan_ops_b200 import _native, checkpoint
-from dandan_ops_b200.fused import FusedProjections, concat_layers, fuse_named_projections
+from dandan_ops_b200.fused import FusedProjections, GateUpSilu, concat_layers, fuse_named_projections, pair_order
 
 
 def _layer(n, k, seed, bias=False, device="cpu"):
@@ -54,6 +54,28 @@ def test_fuse_named_children():
     fused = fuse_named_projections(block, ["gate_proj", "up_proj"])
     assert block.gate_proj_up_proj is fused and not hasattr(block, "gate_proj") and hasattr(block, "down_proj")
     assert fused.names == ["gate_proj", "up_proj"] and fused.out_features == 64
+
+
+def test_pair_order_and_gate_up_state():
+    assert pair_order(16).tolist() == [0, 1, 2, 3, 4, 5, 6, 7, 16, 17, 18, 19, 20, 21, 22, 23,
+                                       8, 9, 10, 11, 12, 13, 14, 15, 24, 25, 26, 27, 28, 29, 30, 31]
+    with pytest.raises(ValueError, match="multiple of 8"):
+        pair_order(12)
+    gate, up = _layer(24, 130, 1, bias=True), _layer(24, 130, 2)
+    fused = GateUpSilu(gate, up)
+    assert fused.op.out_features == 48 and fused.out_features == 24
+    assert torch.equal(fused.op.packed_weight[8:16], up.packed_weight[0:8])
+    assert torch.equal(fused.op.scales[16:24], gate.scales[8:16])
+    assert torch.equal(fused.op.bias[:8], gate.bias[:8]) and torch.count_nonzero(fused.op.bias[8:16]) == 0
+    g2, u2 = fused.unfuse()
+    for a, b in ((g2, gate), (u2, up)):
+        for key in ("packed_weight", "scales", "zeros"):
+            assert torch.equal(getattr(a, key), getattr(b, key))
+    assert torch.equal(g2.bias, gate.bias) and u2.bias is None
+    with pytest.raises(ValueError, match="same number of rows"):
+        GateUpSilu(gate, _layer(16, 130, 3))
+    with pytest.raises(ValueError, match="CUDA FP16"):
+        fused(torch.zeros(2, 130))
 
 
 def test_checkpoint_round_trip_is_unchanged():
@@ -125,3 +147,33 @@ def test_image_cache_hit_equals_repack(tmp_path):
         twin.attach_native_image(fresh[:-16])
     twin.scales.mul_(2)                                                  # state changed: the attached image is dropped
     assert not torch.equal(twin._native_image(), fresh)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [1, 3, 8, 16, 33, 64, 65, 300])
+@pytest.mark.parametrize("rows,k,bias", [(1536, 1024, False), (3072, 1024, True), (1000, 4096, True), (8, 200, False)])
+def test_gate_up_silu_matches_the_separate_launches(m, rows, k, bias):
+    """Fused SiLU(gate)*up against the two projections followed by torch's own FP16 silu and
+    multiply on the GPU (the reference's unfused sequence), and against a CPU restatement."""
+    gate, up = _layer(rows, k, 7 + rows, bias=bias, device="cuda"), _layer(rows, k, 9 + rows, bias=bias, device="cuda")
+    fused = GateUpSilu(gate, up)
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m + rows)).half().cuda()
+    got = fused(x)
+    assert got.shape == (m, rows) and _native.status() == 0
+    g16, u16 = gate(x), up(x)
+    separate = torch.nn.functional.silu(g16) * u16
+    # the two routes may add the K partial sums in a different order: compare within the path's tolerance
+    torch.testing.assert_close(got, separate, atol=2e-3, rtol=4e-3)
+    # on the same FP16 sums the fused arithmetic is the reference's, bit for bit
+    pairs = fused.op(x)
+    again = _native.silu_mul_pairs(pairs)
+    order = pair_order(rows, "cuda")
+    gp, upv = pairs[:, :][:, torch.argsort(order)][:, :rows], pairs[:, torch.argsort(order)][:, rows:]
+    want = torch.nn.functional.silu(gp) * upv
+    mism = (again != want)
+    assert float(mism.float().mean()) <= 1e-3           # torch's exp may differ by an ulp before the FP16 rounding
+    torch.testing.assert_close(again, want, atol=0, rtol=2e-3)
+    if m <= 64:
+        assert torch.equal(got, again)                   # in-kernel epilogue == elementwise kernel on the same sums
+    cpu = (torch.nn.functional.silu(gp.cpu().float()).half().float() * upv.cpu().float()).half()
+    torch.testing.assert_close(again.cpu(), cpu, atol=0, rtol=2e-3)
