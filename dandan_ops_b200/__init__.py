@@ -11,13 +11,13 @@ from .quantization import (dequantize_int4, pack_int4, quantize_int4, unpack_int
                            validate_int4_state)
 from .quantized_linear import BACKENDS, FORMAT_VERSION, QuantizedLinear, quantized_linear
 from .sharded import ColumnShardedLinear, shard_rows
-from .fused import FusedProjections, GateUpSilu, concat_layers, fuse_named_projections
+from .fused import FusedProjections, GateUpSilu, RmsNormLinear, concat_layers, fuse_named_projections
 from . import checkpoint
 from . import ops as _ops
 
 __all__ = ["quantize_int4", "dequantize_int4", "pack_int4", "unpack_int4", "validate_int4_state",
            "QuantizedLinear", "quantized_linear", "BACKENDS", "FORMAT_VERSION",
-           "ColumnShardedLinear", "shard_rows", "FusedProjections", "GateUpSilu", "concat_layers",
+           "ColumnShardedLinear", "shard_rows", "FusedProjections", "GateUpSilu", "RmsNormLinear", "concat_layers",
            "fuse_named_projections", "checkpoint"]
 
 try:

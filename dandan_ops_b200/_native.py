@@ -40,6 +40,10 @@ _SIGNATURES = {
     "b2_w4a16_linear_bias": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_linear_silu_mul": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b2_w4a16_silu_mul_pairs": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "b2_w4a16_rmsnorm_linear": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
+                                       _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_rmsnorm_is_fused": (_int, [_i64, _i64, _i64]),
+    "b2_w4a16_residual_rms_norm": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b2_w4a16_plan": (_int, [_i64, _i64, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int),
                              ctypes.POINTER(_int), ctypes.POINTER(_int)]),
 }
@@ -263,3 +267,41 @@ def silu_mul_pairs(y_pairs):
         _check(lib.b2_w4a16_silu_mul_pairs(y_pairs.data_ptr(), y_pairs.stride(0), out.data_ptr(), out.stride(0),
                                            m, n, _stream()))
     return out
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def residual_rms_norm(x, residual, weight, eps, want_sum=True):
+    """(RMSNorm(x + residual) * weight, fp16(x + residual) or None) for CUDA FP16 [M, K] inputs."""
+    lib = load()
+    m, k = x.shape
+    out = torch.empty((m, k), dtype=torch.float16, device=x.device)
+    summed = torch.empty((m, k), dtype=torch.float16, device=x.device) if want_sum else None
+    with torch.cuda.device(x.device):
+        _check(lib.b2_w4a16_residual_rms_norm(x.data_ptr(), x.stride(0), _ptr(residual),
+                                              residual.stride(0) if residual is not None else 0, weight.data_ptr(),
+                                              float(eps), _ptr(summed), k, out.data_ptr(), k, m, k, _stream()))
+    return out, summed
+
+
+def rmsnorm_linear(x, residual, weight, eps, image, n, k, bias=None, want_sum=True):
+    """y = (RMSNorm(x + residual) * weight) @ W^T (+ bias) and the FP16 sum; one launch when the
+    tile kernel takes the problem, norm kernel + linear otherwise (see include/b2_w4a16.h)."""
+    lib = load()
+    m = x.shape[0]
+    device = x.device
+    y = torch.empty((m, n), dtype=torch.float16, device=device)
+    summed = torch.empty((m, k), dtype=torch.float16, device=device) if want_sum else None
+    if m == 0:
+        return y, summed
+    with torch.cuda.device(device):
+        fused = bool(lib.b2_w4a16_rmsnorm_is_fused(m, n, k))
+        scratch = None if fused else torch.empty((m, k), dtype=torch.float16, device=device)
+        ws = workspace(device, int(lib.b2_w4a16_workspace_bytes(m, n, k)))
+        _check(lib.b2_w4a16_rmsnorm_linear(x.data_ptr(), x.stride(0), _ptr(residual),
+                                           residual.stride(0) if residual is not None else 0, weight.data_ptr(),
+                                           float(eps), _ptr(summed), k, _ptr(scratch), image.data_ptr(), _ptr(bias),
+                                           y.data_ptr(), y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), _stream()))
+    return y, summed

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <atomic>
 #include <climits>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -166,10 +167,24 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 
 }
 
+// Residual + RMSNorm in front of a projection (all pointers null: none).
+struct NormArgs {
+    const void* residual = nullptr;
+    const void* weight = nullptr;
+    void* summed = nullptr;
+    int64_t ldr = 0, lds = 0;
+    float eps = 0.0f;
+};
+
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
-             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0) {
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0,
+             const NormArgs& norm = NormArgs()) {
     b2::TileArgs a;
     a.act = act;
+    a.residual = static_cast<const __half*>(norm.residual);
+    a.norm_w = static_cast<const __half*>(norm.weight);
+    a.summed = static_cast<__half*>(norm.summed);
+    a.ldr = norm.ldr; a.lds = norm.lds; a.eps = norm.eps;
     a.x = static_cast<const __half*>(x);
     a.native = static_cast<const uint8_t*>(native);
     a.y = static_cast<__half*>(y);
@@ -569,6 +584,31 @@ __global__ void silu_mul_pairs_kernel(const __half* in, int64_t ld_in, __half* o
     }
 }
 
+// Standalone residual + RMSNorm: one warp per row, the same arithmetic and summation order as the
+// tile kernel's prologue.  `summed` may alias nothing else; when null the sums pass through `out`.
+__global__ void residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, int64_t ldr,
+                                         const __half* weight, float eps, __half* summed, int64_t lds,
+                                         __half* out, int64_t ldo, int m, int k) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= m) return;
+    const int pieces = k >> 3;
+    __half* sums = summed ? summed + row * lds : out + row * ldo;
+    float sq = 0.0f;
+    for (int cc = lane; cc < pieces; cc += 32) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(x + row * ldx + cc * 8));
+        if (residual) v = b2::add_piece(v, __ldg(reinterpret_cast<const uint4*>(residual + row * ldr + cc * 8)));
+        *reinterpret_cast<uint4*>(sums + cc * 8) = v;
+        sq = b2::sumsq_piece(v, sq);
+    }
+    const float inverse = b2::inverse_rms(b2::warp_sum(sq), k, eps);
+    __syncwarp();
+    for (int cc = lane; cc < pieces; cc += 32)      // every lane re-reads only what it wrote itself
+        *reinterpret_cast<uint4*>(out + row * ldo + cc * 8) =
+            b2::norm_piece(*reinterpret_cast<const uint4*>(sums + cc * 8), inverse,
+                           __ldg(reinterpret_cast<const uint4*>(weight + cc * 8)));
+}
+
 // act = 1: rows g / g+8 of every 16-row tile are a gate/up pair and y gets n/2 columns.
 int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                 int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
@@ -631,6 +671,74 @@ int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, con
                              int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                              int64_t workspace_bytes, void* stream) {
     return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 1);
+}
+
+int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, int64_t ldr, const void* norm_weight,
+                            float eps, void* summed, int64_t lds, void* xn_scratch, const void* native,
+                            const void* bias_fp16, void* y, int64_t ldy, int64_t m, int64_t n, int64_t k,
+                            void* workspace, int64_t workspace_bytes, void* stream) {
+    if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
+    if (int rc = check_dims(n, k)) return rc;
+    if (m == 0) return B2_OK;
+    if (!x || !norm_weight || !native || !y) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (!(eps >= 0.0f) || !std::isfinite(eps)) return fail(B2_ERR_ARGUMENT, "eps must be finite and non-negative");
+    if (k % 8 != 0 || ldx % 8 != 0 || (residual && ldr % 8 != 0) || (summed && lds % 8 != 0))
+        return fail(B2_ERR_UNSUPPORTED, "the RMSNorm prologue needs K and the row strides to be multiples of 8");
+    for (const void* p : {x, residual, norm_weight, static_cast<const void*>(summed), static_cast<const void*>(xn_scratch)})
+        if (p && reinterpret_cast<uintptr_t>(p) % 16) return fail(B2_ERR_ARGUMENT, "RMSNorm operands must be 16-byte aligned");
+    if (ldx < k || (residual && ldr < k) || (summed && lds < k))
+        return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+    if (m > INT_MAX - 128 || m * k > INT_MAX || m * n > INT_MAX)
+        return fail(B2_ERR_RANGE, "W4A16 dimensions exceed the kernel index range");
+    DeviceInfo dev;
+    if (int rc = device_info(dev)) return rc;
+    if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
+    const b2::Dims d = b2::make_dims(n, k);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (tile_applicable(m, d)) {         // fused: the tile kernel normalizes its staged copy of x
+        if (bias_fp16 && reinterpret_cast<uintptr_t>(bias_fp16) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
+        if (reinterpret_cast<uintptr_t>(native) % 16) return fail(B2_ERR_ARGUMENT, "native image must be 16-byte aligned");
+        if (ldy < n) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+        NormArgs norm;
+        norm.residual = residual; norm.weight = norm_weight; norm.summed = summed;
+        norm.ldr = ldr; norm.lds = lds; norm.eps = eps;
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, true, s, bias_fp16, 0, norm);
+    }
+    if (!xn_scratch) return fail(B2_ERR_ARGUMENT, "this problem runs the norm as its own kernel and needs xn_scratch [M, K]");
+    const int warps = 8;
+    residual_rms_norm_kernel<<<unsigned((m + warps - 1) / warps), warps * 32, 0, s>>>(
+        static_cast<const __half*>(x), ldx, static_cast<const __half*>(residual), ldr,
+        static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
+        static_cast<__half*>(xn_scratch), k, int(m), int(k));
+    if (int rc = after_launch("residual_rms_norm_kernel")) return rc;
+    return linear_impl(xn_scratch, k, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 0);
+}
+
+int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual, int64_t ldr, const void* norm_weight,
+                               float eps, void* summed, int64_t lds, void* out, int64_t ldo, int64_t m, int64_t k,
+                               void* stream) {
+    if (m < 0 || k <= 0) return fail(B2_ERR_ARGUMENT, "m >= 0 and k > 0 expected");
+    if (m == 0) return B2_OK;
+    if (!x || !norm_weight || !out) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (!(eps >= 0.0f) || !std::isfinite(eps)) return fail(B2_ERR_ARGUMENT, "eps must be finite and non-negative");
+    if (k % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0 || (residual && ldr % 8 != 0) || (summed && lds % 8 != 0))
+        return fail(B2_ERR_UNSUPPORTED, "RMSNorm needs K and the row strides to be multiples of 8");
+    for (const void* p : {x, residual, norm_weight, static_cast<const void*>(summed), static_cast<const void*>(out)})
+        if (p && reinterpret_cast<uintptr_t>(p) % 16) return fail(B2_ERR_ARGUMENT, "RMSNorm operands must be 16-byte aligned");
+    if (ldx < k || ldo < k || (residual && ldr < k) || (summed && lds < k))
+        return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
+    if (m > INT_MAX - 128 || k > INT_MAX - 64 || m * k > INT_MAX) return fail(B2_ERR_RANGE, "dimensions exceed the kernel index range");
+    const int warps = 8;
+    residual_rms_norm_kernel<<<unsigned((m + warps - 1) / warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), ldx, static_cast<const __half*>(residual), ldr,
+        static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
+        static_cast<__half*>(out), ldo, int(m), int(k));
+    return after_launch("residual_rms_norm_kernel");
+}
+
+int b2_w4a16_rmsnorm_is_fused(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || check_dims(n, k) != B2_OK || k % 8 != 0) return 0;
+    return tile_applicable(m, b2::make_dims(n, k)) ? 1 : 0;
 }
 
 int b2_w4a16_silu_mul_pairs(const void* y_pairs, int64_t ld_in, void* out, int64_t ld_out, int64_t m, int64_t n,

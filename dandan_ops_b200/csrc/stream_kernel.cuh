@@ -117,6 +117,55 @@ __device__ __forceinline__ __half finish_output(float acc, const __half* bias, i
     const __half h = __float2half_rn(acc);
     return bias ? __hadd(h, bias[n]) : h;
 }
+// Residual add + RMSNorm on 16-byte pieces (eight FP16 values), with the reference's rounding
+// order (dandan_ops/csrc/elementwise.cu:39-62, dandan_ops/elementwise.py:118-120): the sum is
+// rounded to FP16 first, the normalized value is rounded to FP16 before the weight multiplies it.
+__device__ __forceinline__ uint4 add_piece(const uint4& x, const uint4& r) {
+    const __half2* a = reinterpret_cast<const __half2*>(&x);
+    const __half2* b = reinterpret_cast<const __half2*>(&r);
+    uint4 out;
+    __half2* o = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fa = __half22float2(a[i]), fb = __half22float2(b[i]);
+        o[i] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+    }
+    return out;
+}
+__device__ __forceinline__ float sumsq_piece(const uint4& v, float acc) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        acc = fmaf(f.x, f.x, acc);
+        acc = fmaf(f.y, f.y, acc);
+    }
+    return acc;
+}
+__device__ __forceinline__ uint4 norm_piece(const uint4& v, float inverse, const uint4& w) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    const __half2* g = reinterpret_cast<const __half2*>(&w);
+    uint4 out;
+    __half2* o = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        const __half2 n = __floats2half2_rn(f.x * inverse, f.y * inverse);
+        const float2 fn = __half22float2(n), fw = __half22float2(g[i]);
+        o[i] = __floats2half2_rn(fn.x * fw.x, fn.y * fw.y);
+    }
+    return out;
+}
+// Sum over a warp in a fixed order (the same in the fused prologue and in the standalone kernel).
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float inverse_rms(float sumsq, int k, float eps) {
+    return 1.0f / sqrtf(sumsq / float(k) + eps);
+}
+
 // SiLU(gate) * up on FP16 values with the reference's rounding order: the activation is rounded
 // to FP16 before the multiplication (dandan_ops/csrc/elementwise.cu:70-73,
 // `torch.nn.functional.silu(gate) * up` on the CPU route).

@@ -32,6 +32,14 @@ struct TileArgs {
     int n16, kb;
     int warps;              // warps per CTA = min(16, 2*kb)
     int act;                // as StreamArgs::act
+    // RMSNorm prologue (norm_w != null; needs the vectorised x path): the CTA multiplies by
+    // RMSNorm(x + residual) * norm_w instead of x.  residual may be null; CTA 0 stores the FP16
+    // sum to `summed` if that is not null.
+    const __half* residual;
+    const __half* norm_w;
+    __half* summed;
+    int64_t ldr, lds;
+    float eps;
 };
 
 __host__ __device__ constexpr int tile_smem_bytes(int kb, int mt, int warps) {
@@ -74,6 +82,40 @@ w4a16_tile_kernel(const TileArgs a) {
             const int k = cc * 8;
             stage_piece<XVEC, false>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16, a.x + int64_t(m) * a.ldx + k,
                               m < a.m && k < a.k, k, a.k);
+        }
+    }
+    if (XVEC && a.norm_w) {
+        // The weight copies are in flight; the three passes over the staged rows hide behind them.
+        const int pieces_per_row = a.kb * 32;
+        const int total = MP * pieces_per_row;
+        auto piece_at = [&](int m, int cc) { return reinterpret_cast<uint4*>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16); };
+        __syncthreads();
+        if (a.residual || a.summed) {
+            for (int i = threadIdx.x; i < total; i += blockDim.x) {
+                const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
+                if (m < a.m && cc * 8 < a.k) {
+                    uint4 v = *piece_at(m, cc);
+                    if (a.residual) {
+                        v = add_piece(v, __ldg(reinterpret_cast<const uint4*>(a.residual + int64_t(m) * a.ldr + cc * 8)));
+                        *piece_at(m, cc) = v;
+                    }
+                    if (a.summed && blockIdx.x == 0) *reinterpret_cast<uint4*>(a.summed + int64_t(m) * a.lds + cc * 8) = v;
+                }
+            }
+            __syncthreads();
+        }
+        float* inverse = reinterpret_cast<float*>(red);            // the reduction tiles are not in use yet
+        for (int m = warp; m < a.m; m += a.warps) {
+            float sq = 0.0f;
+            for (int cc = lane; cc < pieces_per_row; cc += 32) sq = sumsq_piece(*piece_at(m, cc), sq);   // zeros beyond K
+            sq = warp_sum(sq);
+            if (lane == 0) inverse[m] = inverse_rms(sq, a.k, a.eps);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < total; i += blockDim.x) {
+            const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
+            if (m < a.m && cc * 8 < a.k)
+                *piece_at(m, cc) = norm_piece(*piece_at(m, cc), inverse[m], __ldg(reinterpret_cast<const uint4*>(a.norm_w + cc * 8)));
         }
     }
     __syncthreads();        // x staged; barrier initialisation visible to every waiter

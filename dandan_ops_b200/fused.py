@@ -139,6 +139,47 @@ class GateUpSilu(nn.Module):
         return tuple(out)
 
 
+class RmsNormLinear(nn.Module):
+    """`forward(x, residual=None) -> (y, summed)`: residual add + RMSNorm + projection.
+
+    The step in front of the qkv projection of a decoder layer (the reference runs
+    `residual_rms_norm` as its own kernel, dandan_ops/elementwise.py:156-165).  For decode batches
+    on small layers the projection kernel normalizes its own staged copy of x - one launch; other
+    sizes run a norm kernel with the same arithmetic and then the projection."""
+
+    def __init__(self, norm_weight, layer, eps=1e-5):
+        super().__init__()
+        if not isinstance(layer, QuantizedLinear):
+            raise TypeError("layer must be a QuantizedLinear")
+        if norm_weight.ndim != 1 or norm_weight.shape[0] != layer.in_features:
+            raise ValueError("norm weight must have in_features elements")
+        if layer.in_features % 8:
+            raise ValueError("the RMSNorm prologue needs in_features to be a multiple of 8")
+        eps = float(eps)
+        if not (eps >= 0.0) or eps == float("inf"):
+            raise ValueError("eps must be finite, nonnegative and representable as FP32")
+        self.op = layer
+        self.eps = eps
+        self.register_buffer("norm_weight", norm_weight.detach().to(torch.float16).contiguous())
+        self.in_features, self.out_features = layer.in_features, layer.out_features
+        self.eval()
+
+    def forward(self, x, residual=None):
+        for t in (x, residual):
+            if t is None:
+                continue
+            if not isinstance(t, torch.Tensor) or t.ndim != 2 or t.shape[1] != self.in_features:
+                raise ValueError("x and residual must have shape [M, in_features]")
+            if t.dtype != torch.float16 or t.device != self.op.packed_weight.device or not t.is_cuda:
+                raise ValueError("the RMSNorm prologue requires CUDA FP16 inputs on the layer's device")
+        if residual is not None and residual.shape != x.shape:
+            raise ValueError("x and residual must have the same shape")
+        x = x.contiguous()
+        residual = None if residual is None else residual.contiguous()
+        return _native.rmsnorm_linear(x, residual, self.norm_weight, self.eps, self.op._native_image(),
+                                      self.out_features, self.in_features, bias=self.op._bias_fp16())
+
+
 def fuse_named_projections(parent, names, fused_name=None):
     """Replace the child modules `names` of `parent` (QuantizedLinear layers or adapters that
     hold one in `.op`) by one FusedProjections child called `fused_name` (default: the names

@@ -8,7 +8,7 @@ import torch
 
 import dandan_ops_b200 as ops
 from dandan_ops_b200 import _native, checkpoint
-from dandan_ops_b200.fused import FusedProjections, GateUpSilu, concat_layers, fuse_named_projections, pair_order
+from dandan_ops_b200.fused import FusedProjections, GateUpSilu, RmsNormLinear, concat_layers, fuse_named_projections, pair_order
 
 
 def _layer(n, k, seed, bias=False, device="cpu"):
@@ -177,3 +177,54 @@ def test_gate_up_silu_matches_the_separate_launches(m, rows, k, bias):
         assert torch.equal(got, again)                   # in-kernel epilogue == elementwise kernel on the same sums
     cpu = (torch.nn.functional.silu(gp.cpu().float()).half().float() * upv.cpu().float()).half()
     torch.testing.assert_close(again.cpu(), cpu, atol=0, rtol=2e-3)
+
+
+def test_rmsnorm_linear_argument_checks():
+    layer = _layer(16, 64, 1)
+    with pytest.raises(ValueError, match="in_features elements"):
+        RmsNormLinear(torch.ones(63), layer)
+    with pytest.raises(ValueError, match="multiple of 8"):
+        RmsNormLinear(torch.ones(60), _layer(16, 60, 2))
+    with pytest.raises(ValueError, match="eps"):
+        RmsNormLinear(torch.ones(64), layer, eps=-1.0)
+    mod = RmsNormLinear(torch.ones(64), layer, eps=1e-6)
+    assert mod.norm_weight.dtype == torch.float16 and "norm_weight" in mod.state_dict()
+    with pytest.raises(ValueError, match="CUDA FP16"):
+        mod(torch.zeros(2, 64, dtype=torch.float16))
+
+
+def _rms_reference(summed, weight, eps):
+    """The reference's CPU formula (dandan_ops/elementwise.py:118-120)."""
+    work = summed.float()
+    return (work * torch.rsqrt(work.square().mean(-1, keepdim=True) + eps)).to(summed.dtype) * weight
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 1024), (8, 4096, 1024), (16, 1024, 2048), (5, 1000, 1032),
+                                   (8, 24576, 4096), (40, 2048, 1024), (300, 1536, 1024)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_rmsnorm_prologue_matches_norm_then_projection(m, n, k, with_residual):
+    gen = torch.Generator().manual_seed(m + n + k)
+    layer = _layer(n, k, 3 + n, bias=(n == 1000), device="cuda")
+    weight = (1.0 + 0.1 * torch.randn(k, generator=gen)).half().cuda()
+    x = torch.randn(m, k, generator=gen).half().cuda()
+    residual = torch.randn(m, k, generator=gen).half().cuda() if with_residual else None
+    mod = RmsNormLinear(weight, layer, eps=1e-6)
+    y, summed = mod(x, residual)
+    assert _native.status() == 0
+    want_sum = (x + residual) if with_residual else x
+    assert torch.equal(summed, want_sum)                                   # FP16 add, one rounding
+    xn, summed2 = _native.residual_rms_norm(x, residual, weight, 1e-6)
+    assert torch.equal(summed2, want_sum)
+    assert torch.equal(y, layer(xn))           # fused prologue == norm kernel followed by the projection, bit for bit
+    # the norm itself against the reference's CPU formula: the FP32 sum of squares is added in another
+    # order, so a normalized value may round to the neighbouring FP16 number now and then
+    ref = _rms_reference(want_sum.cpu(), weight.cpu(), 1e-6)
+    torch.testing.assert_close(xn.cpu(), ref, atol=1e-6, rtol=2e-3)
+    assert float((xn.cpu() != ref).float().mean()) < 5e-3
+    expected = ref.double() @ layer.dequantize().half().double().t().cpu()
+    if layer.bias is not None:
+        expected = (expected.float().half() + layer.bias.half().cpu()).double()
+    torch.testing.assert_close(y.cpu().double(), expected, atol=4e-3, rtol=4e-3)
+    fused_expected = bool(_native.load().b2_w4a16_rmsnorm_is_fused(m, n, k))
+    assert fused_expected == (layer.execution_info(x)["kernel_plan"]["route"] == "b200_tile")
