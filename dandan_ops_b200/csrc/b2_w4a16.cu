@@ -158,7 +158,8 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
     cudaGetDevice(&dev);
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemLimit);
+        // + 16 KB: the RMSNorm prologue stages the norm weight (kb * 512 bytes) on top of the tile's own need
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemLimit + 16 * 1024);
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
@@ -194,7 +195,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
     a.warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
     const int mt = rows <= 8 ? 1 : 2;
-    const int smem = b2::tile_smem_bytes(d.kb, mt, a.warps);
+    const int smem = b2::tile_smem_bytes(d.kb, mt, a.warps) + (norm.weight ? d.kb * 512 : 0);   // + staged norm weight
     if (mt == 1) return xvec ? launch_tile_one<1, true>(a, smem, s) : launch_tile_one<1, false>(a, smem, s);
     return xvec ? launch_tile_one<2, true>(a, smem, s) : launch_tile_one<2, false>(a, smem, s);
 }
@@ -584,6 +585,11 @@ __global__ void silu_mul_pairs_kernel(const __half* in, int64_t ld_in, __half* o
     }
 }
 
+// Every CTA of the tile kernel normalizes all rows of x for itself, so the prologue's cost grows
+// with M while the separate norm kernel's does not: measured on 4096 x 1024, the fused form wins
+// up to 8 rows (4.6 vs 5.5 us at M = 1, 5.9 vs 6.8 at M = 8) and loses at 16 (8.9 vs 7.2).
+bool norm_fused(int64_t m, const b2::Dims& d) { return m <= 8 && tile_applicable(m, d); }
+
 // Standalone residual + RMSNorm: one warp per row, the same arithmetic and summation order as the
 // tile kernel's prologue.  `summed` may alias nothing else; when null the sums pass through `out`.
 __global__ void residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, int64_t ldr,
@@ -595,18 +601,43 @@ __global__ void residual_rms_norm_kernel(const __half* x, int64_t ldx, const __h
     const int pieces = k >> 3;
     __half* sums = summed ? summed + row * lds : out + row * ldo;
     float sq = 0.0f;
-    for (int cc = lane; cc < pieces; cc += 32) {
-        uint4 v = __ldg(reinterpret_cast<const uint4*>(x + row * ldx + cc * 8));
-        if (residual) v = b2::add_piece(v, __ldg(reinterpret_cast<const uint4*>(residual + row * ldr + cc * 8)));
-        *reinterpret_cast<uint4*>(sums + cc * 8) = v;
-        sq = b2::sumsq_piece(v, sq);
+    constexpr int kBatch = 8;               // loads in flight per lane; the sum keeps the order of the pieces
+    for (int c0 = lane; c0 < pieces; c0 += 32 * kBatch) {
+        uint4 v[kBatch], r[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int cc = c0 + 32 * j;
+            v[j] = cc < pieces ? __ldg(reinterpret_cast<const uint4*>(x + row * ldx + cc * 8)) : make_uint4(0, 0, 0, 0);
+            r[j] = (cc < pieces && residual) ? __ldg(reinterpret_cast<const uint4*>(residual + row * ldr + cc * 8)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int cc = c0 + 32 * j;
+            if (cc < pieces) {
+                if (residual) v[j] = b2::add_piece(v[j], r[j]);
+                *reinterpret_cast<uint4*>(sums + cc * 8) = v[j];
+                sq = b2::sumsq_piece(v[j], sq);
+            }
+        }
     }
     const float inverse = b2::inverse_rms(b2::warp_sum(sq), k, eps);
     __syncwarp();
-    for (int cc = lane; cc < pieces; cc += 32)      // every lane re-reads only what it wrote itself
-        *reinterpret_cast<uint4*>(out + row * ldo + cc * 8) =
-            b2::norm_piece(*reinterpret_cast<const uint4*>(sums + cc * 8), inverse,
-                           __ldg(reinterpret_cast<const uint4*>(weight + cc * 8)));
+    for (int c0 = lane; c0 < pieces; c0 += 32 * kBatch) {      // every lane re-reads only what it wrote itself
+        uint4 v[kBatch], w[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int cc = c0 + 32 * j;
+            if (cc < pieces) {
+                v[j] = *reinterpret_cast<const uint4*>(sums + cc * 8);
+                w[j] = __ldg(reinterpret_cast<const uint4*>(weight + cc * 8));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int cc = c0 + 32 * j;
+            if (cc < pieces) *reinterpret_cast<uint4*>(out + row * ldo + cc * 8) = b2::norm_piece(v[j], inverse, w[j]);
+        }
+    }
 }
 
 // act = 1: rows g / g+8 of every 16-row tile are a gate/up pair and y gets n/2 columns.
@@ -695,7 +726,7 @@ int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, in
     if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     const b2::Dims d = b2::make_dims(n, k);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (tile_applicable(m, d)) {         // fused: the tile kernel normalizes its staged copy of x
+    if (norm_fused(m, d)) {              // fused: the tile kernel normalizes its staged copy of x
         if (bias_fp16 && reinterpret_cast<uintptr_t>(bias_fp16) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
         if (reinterpret_cast<uintptr_t>(native) % 16) return fail(B2_ERR_ARGUMENT, "native image must be 16-byte aligned");
         if (ldy < n) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
@@ -738,7 +769,7 @@ int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual,
 
 int b2_w4a16_rmsnorm_is_fused(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || check_dims(n, k) != B2_OK || k % 8 != 0) return 0;
-    return tile_applicable(m, b2::make_dims(n, k)) ? 1 : 0;
+    return norm_fused(m, b2::make_dims(n, k)) ? 1 : 0;
 }
 
 int b2_w4a16_silu_mul_pairs(const void* y_pairs, int64_t ld_in, void* out, int64_t ld_out, int64_t m, int64_t n,

@@ -370,12 +370,16 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
                 for (int cc = 0; cc < MT / 64; ++cc) {
                     uint32_t v[32];
                     load_chunk(cc, v);
-                    __half* row = reinterpret_cast<__half*>(stage + cc * 32 * 64) + lane;
+                    uint16_t* row = reinterpret_cast<uint16_t*>(stage + cc * 32 * 64) + lane;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        __half hv = __float2half_rn(__uint_as_float(v[e]));
-                        if (a.bias) hv = __hadd(hv, bias);
-                        row[e * 32] = hv;
+                    for (int e = 0; e < 32; e += 2) {          // packed FP32 -> FP16 conversion, two rows of y at a time
+                        uint32_t p = pack_f16(__uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                        if (a.bias) {
+                            const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&p), __half2half2(bias));
+                            p = *reinterpret_cast<const uint32_t*>(&sum);
+                        }
+                        row[e * 32] = uint16_t(p);
+                        row[(e + 1) * 32] = uint16_t(p >> 16);
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores -> TMA store
@@ -394,12 +398,15 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
                     if (n_ok) {
                         __half* dst = a.y + int64_t(m0 + col) * a.ldy + n;
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            if (m0 + col + e < a.m) {
-                                __half hv = __float2half_rn(__uint_as_float(v[e]));
-                                if (a.bias) hv = __hadd(hv, bias);
-                                dst[int64_t(e) * a.ldy] = hv;
+                        for (int e = 0; e < 32; e += 2) {
+                            uint32_t p = pack_f16(__uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+                            if (a.bias) {
+                                const __half2 sum = __hadd2(*reinterpret_cast<const __half2*>(&p), __half2half2(bias));
+                                p = *reinterpret_cast<const uint32_t*>(&sum);
                             }
+                            uint16_t* out16 = reinterpret_cast<uint16_t*>(dst);
+                            if (m0 + col + e < a.m) out16[int64_t(e) * a.ldy] = uint16_t(p);
+                            if (m0 + col + e + 1 < a.m) out16[int64_t(e + 1) * a.ldy] = uint16_t(p >> 16);
                         }
                     }
                 }

@@ -120,41 +120,57 @@ __device__ __forceinline__ __half finish_output(float acc, const __half* bias, i
 // Residual add + RMSNorm on 16-byte pieces (eight FP16 values), with the reference's rounding
 // order (dandan_ops/csrc/elementwise.cu:39-62, dandan_ops/elementwise.py:118-120): the sum is
 // rounded to FP16 first, the normalized value is rounded to FP16 before the weight multiplies it.
+// FP16 -> FP32 conversions go through the mixed-precision FMA-pipe instructions (full rate); the
+// plain cvt runs at a quarter of that and made these helpers the bottleneck of the prologue.
+__device__ __forceinline__ void unpack_f32(uint32_t h2, float& lo, float& hi) {     // exact, keeps the sign of zero
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "add.rn.f32.f16 %0, l, 0f80000000;\n\tadd.rn.f32.f16 %1, h, 0f80000000;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(h2));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t add_pair(uint32_t a, uint32_t b) {               // fp16(float(a) + float(b))
+    float alo, ahi, lo, hi;
+    unpack_f32(a, alo, ahi);
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+        "add.rn.f32.f16 %0, l, %3;\n\tadd.rn.f32.f16 %1, h, %4;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(b), "f"(alo), "f"(ahi));
+    return pack_f16(lo, hi);
+}
+__device__ __forceinline__ uint32_t mul_pair(uint32_t a, uint32_t b) {               // fp16(float(a) * float(b)), product exact in FP32
+    float lo, hi;
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\tmov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, al, bl, 0f80000000;\n\tfma.rn.f32.f16 %1, ah, bh, 0f80000000;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(a), "r"(b));
+    return pack_f16(lo, hi);
+}
 __device__ __forceinline__ uint4 add_piece(const uint4& x, const uint4& r) {
-    const __half2* a = reinterpret_cast<const __half2*>(&x);
-    const __half2* b = reinterpret_cast<const __half2*>(&r);
-    uint4 out;
-    __half2* o = reinterpret_cast<__half2*>(&out);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 fa = __half22float2(a[i]), fb = __half22float2(b[i]);
-        o[i] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
-    }
-    return out;
+    return make_uint4(add_pair(x.x, r.x), add_pair(x.y, r.y), add_pair(x.z, r.z), add_pair(x.w, r.w));
 }
 __device__ __forceinline__ float sumsq_piece(const uint4& v, float acc) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]);
-        acc = fmaf(f.x, f.x, acc);
-        acc = fmaf(f.y, f.y, acc);
+        float lo, hi;
+        unpack_f32(w[i], lo, hi);
+        acc = fmaf(lo, lo, acc);
+        acc = fmaf(hi, hi, acc);
     }
     return acc;
 }
 __device__ __forceinline__ uint4 norm_piece(const uint4& v, float inverse, const uint4& w) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-    const __half2* g = reinterpret_cast<const __half2*>(&w);
-    uint4 out;
-    __half2* o = reinterpret_cast<__half2*>(&out);
+    const uint32_t a[4] = {v.x, v.y, v.z, v.w}, g[4] = {w.x, w.y, w.z, w.w};
+    uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]);
-        const __half2 n = __floats2half2_rn(f.x * inverse, f.y * inverse);
-        const float2 fn = __half22float2(n), fw = __half22float2(g[i]);
-        o[i] = __floats2half2_rn(fn.x * fw.x, fn.y * fw.y);
+        float lo, hi;
+        unpack_f32(a[i], lo, hi);
+        o[i] = mul_pair(pack_f16(lo * inverse, hi * inverse), g[i]);
     }
-    return out;
+    return make_uint4(o[0], o[1], o[2], o[3]);
 }
 // Sum over a warp in a fixed order (the same in the fused prologue and in the standalone kernel).
 __device__ __forceinline__ float warp_sum(float v) {

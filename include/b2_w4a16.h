@@ -171,7 +171,7 @@ int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, con
  * + eps)) * norm_weight),  y = xn @ W^T (+ bias) - the rounding order of the reference's
  * `residual_rms_norm` (dandan_ops/elementwise.py:156-165, dandan_ops/csrc/elementwise.cu:39-62).
  * `summed` (optional, [M, K], row stride lds) receives s for the residual stream.
- * For problems the tile kernel takes (b2_w4a16_rmsnorm_is_fused() == 1: M <= 16, small layers) the
+ * For problems the tile kernel takes (b2_w4a16_rmsnorm_is_fused() == 1: M <= 8, small layers) the
  * kernel normalizes its own shared-memory copy of x while the weight copies are in flight and no
  * extra launch happens; otherwise the norm runs as one kernel into `xn_scratch` ([M, K] FP16,
  * row stride K, required then) followed by b2_w4a16_linear.  Both paths use the same arithmetic

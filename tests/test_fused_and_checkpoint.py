@@ -227,4 +227,4 @@ def test_rmsnorm_prologue_matches_norm_then_projection(m, n, k, with_residual):
         expected = (expected.float().half() + layer.bias.half().cpu()).double()
     torch.testing.assert_close(y.cpu().double(), expected, atol=4e-3, rtol=4e-3)
     fused_expected = bool(_native.load().b2_w4a16_rmsnorm_is_fused(m, n, k))
-    assert fused_expected == (layer.execution_info(x)["kernel_plan"]["route"] == "b200_tile")
+    assert fused_expected == (m <= 8 and layer.execution_info(x)["kernel_plan"]["route"] == "b200_tile")
