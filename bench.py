@@ -329,40 +329,45 @@ def per_shape_detail(spec, layers, x_dev, stream, device):
     part of the timed step, among them the prefill sizes that run on the tcgen05 GEMM."""
     out = []
     gen = torch.Generator().manual_seed(spec["seed"] + 6)
+    all_ms = sorted(set(spec["ms"]) | set(spec.get("detail_ms", [])))
     with torch.cuda.stream(stream):
-        for si, (name, n_full, k) in enumerate(spec["shapes"]):
-            column = [row[si] for row in layers if row[si][3] is not None]
-            if not column:
-                continue
-            n = column[0][1]
-            reps = max(1, int(300e6 // max(1.0, len(column) * weight_bytes(n, k))))
-            for m in sorted(set(spec["ms"]) | set(spec.get("detail_ms", []))):
-                x = x_dev.get((m, k))
-                if x is None:
-                    x = torch.randn(m, k, generator=gen).half().to(device)
-                if m > 64:
-                    reps = 1
-                for _, _, _, layer in column:
-                    layer(x)
-                stream.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    for _ in range(reps):
-                        for _, _, _, layer in column:
-                            layer(x)
-                samples = []
-                for _ in range(7):
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record(stream)
-                    graph.replay()
-                    e1.record(stream)
+        # Decode sizes of every projection first, the prefill sizes last: seconds of GEMM at the
+        # power cap lower the SM clock for a while, which would tax whatever is timed right after.
+        for prefill in (False, True):
+            for si, (name, n_full, k) in enumerate(spec["shapes"]):
+                column = [row[si] for row in layers if row[si][3] is not None]
+                if not column:
+                    continue
+                n = column[0][1]
+                for m in all_ms:
+                    if (m > 64) != prefill:
+                        continue
+                    reps = 1 if prefill else max(1, int(300e6 // max(1.0, len(column) * weight_bytes(n, k))))
+                    x = x_dev.get((m, k))
+                    if x is None:
+                        x = torch.randn(m, k, generator=gen).half().to(device)
+                    for _, _, _, layer in column:
+                        layer(x)
                     stream.synchronize()
-                    samples.append(e0.elapsed_time(e1) * 1e3 / (reps * len(column)))
-                us = statistics.median(samples)
-                out.append({"proj": name, "N": n, "K": k, "M": m, "us": round(us, 2),
-                            "kernel": layer.execution_info(x)["implementation"],
-                            "weight_GBps": round(weight_bytes(n, k) / us / 1e3, 1),
-                            "TFLOPS": round(2.0 * m * n * k / us / 1e6, 2)})
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        for _ in range(reps):
+                            for _, _, _, layer in column:
+                                layer(x)
+                    samples = []
+                    for _ in range(7):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        graph.replay()
+                        e1.record(stream)
+                        stream.synchronize()
+                        samples.append(e0.elapsed_time(e1) * 1e3 / (reps * len(column)))
+                    us = statistics.median(samples)
+                    out.append({"proj": name, "N": n, "K": k, "M": m, "us": round(us, 2),
+                                "kernel": layer.execution_info(x)["implementation"],
+                                "weight_GBps": round(weight_bytes(n, k) / us / 1e3, 1),
+                                "TFLOPS": round(2.0 * m * n * k / us / 1e6, 2)})
+    out.sort(key=lambda r: ([s[0] for s in spec["shapes"]].index(r["proj"]), r["M"]))
     return out
 
 
