@@ -359,8 +359,40 @@ inline int max_splits(const GemmShape& g, int64_t m, int64_t n, int kb) {
     return std::max(1, std::min(kMaxSplits, kb / 4));
 }
 
-inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms) {
-    const int forced = g_forced_shape.load(std::memory_order_relaxed);
+// Can this device co-schedule the pair kernel's two-CTA clusters at all (asked once per device)?
+// A partition without two free SMs in one cluster-capable group answers no, and the GEMM then
+// stays on the single-CTA shapes.
+bool pair_available() {
+    static std::atomic<int> state[64];          // 0 = not asked yet, 1 = yes, 2 = no
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::atomic<int>& st = state[dev & 63];
+    const int known = st.load(std::memory_order_acquire);
+    if (known) return known == 1;
+    auto kernel = b2::w4a16_gemm_pair_kernel<192, true>;
+    constexpr int smem = b2::pair_smem_bytes<192>();
+    bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
+    if (ok) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2, 1, 1);
+        cfg.blockDim = dim3(b2::kPairThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        ok = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters > 0;
+    }
+    if (!ok) cudaGetLastError();                // clear the error of a failed query
+    st.store(ok ? 1 : 2, std::memory_order_release);
+    return ok;
+}
+
+inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms, bool pairs_ok = true) {
+    const int forced = pairs_ok || g_forced_shape.load(std::memory_order_relaxed) <= 3
+                           ? g_forced_shape.load(std::memory_order_relaxed) : 0;
     const int forced_splits = g_forced_splits.load(std::memory_order_relaxed);
     const int64_t pairs = sms >= 2 ? sms / 2 : 1;
     // waves x cost per tile and SM (times four).  Two co-resident 192-row tiles cost 21 each; one
@@ -378,6 +410,7 @@ inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms) {
     int64_t best_cost = INT64_MAX;
     for (int i = 0; i < 5; ++i) {
         if (forced ? i != forced - 1 : (m <= 128 && i != 0)) continue;
+        if (!pairs_ok && kGemmShapes[i].pair_mt) continue;
         GemmShape g = kGemmShapes[i];
         const int smax = max_splits(g, m, n, kb);
         for (int sp = 1; sp <= smax; ++sp) {
@@ -399,7 +432,7 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(m)};
     const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
-    GemmShape shape = gemm_shape(m, d.n, d.kb, sms);
+    GemmShape shape = gemm_shape(m, d.n, d.kb, sms, pair_available());
     if (B2_W4A16_TICKET_BYTES + shape.partial_bytes(m, d.n) > workspace_bytes) shape.splits = 1;   // no room: one CTA per tile
     const int pair_mt = shape.pair_mt;
     const cuuint32_t box[2] = {cuuint32_t(b2::kGemmBK), pair_mt ? cuuint32_t(pair_mt / 2) : 128u};

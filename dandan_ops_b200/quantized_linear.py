@@ -134,6 +134,8 @@ class QuantizedLinear(torch.nn.Module):
         self._image_key = None
         self._bias16 = None
         self._bias16_key = None
+        self._checked_key = None
+        self._checked_device = None
         self.eval()
         if self.packed_weight.is_cuda and group_size == 64:
             self._native_image()
@@ -270,7 +272,30 @@ class QuantizedLinear(torch.nn.Module):
             raise ValueError("dequantize " + CUDA_ONLY.replace(" FP16", ""))
         return _native.dequantize(self._native_image(), self.out_features, self.in_features)
 
+    def _forward_key(self):
+        bias = self.bias
+        return (self.packed_weight.data_ptr(), self.scales.data_ptr(), self.zeros.data_ptr(),
+                self.packed_weight._version, self.scales._version, self.zeros._version,
+                id(self.packed_weight), id(self.scales), id(self.zeros),
+                self.in_features, self.group_size, self.backend,
+                None if bias is None else (bias.data_ptr(), bias._version, bias.dtype))
+
     def forward(self, x):
+        # Per-token fast path: the metadata checks below depend only on the layer's state, so they
+        # are repeated only when a state tensor was replaced or written (data pointer / version
+        # counter), an attribute was reassigned, or x is not the plain CUDA FP16 case.
+        key = self._forward_key()
+        if (key == self._checked_key and type(x) is torch.Tensor and x.dtype is torch.float16 and x.ndim == 2
+                and x.shape[1] == self.in_features and x.device == self._checked_device
+                and not (x.requires_grad and torch.is_grad_enabled())):
+            return _engine(x, self._image, self.out_features, self.in_features, self._bias_fp16())
+        y = self._forward_checked(x)
+        if self.backend in ("auto", "cuda", "tensorcore", "naive") and not self.scales.requires_grad \
+                and self._image is not None:
+            self._checked_key, self._checked_device = self._forward_key(), self.packed_weight.device
+        return y
+
+    def _forward_checked(self, x):
         validate_int4_state(self.packed_weight, self.scales, self.zeros, self.in_features, self.group_size)
         if not isinstance(x, torch.Tensor) or x.ndim != 2 or x.shape[1] != self.in_features:
             raise ValueError("x must have shape [M, in_features]")

@@ -458,3 +458,28 @@ def test_fused_bias_keeps_the_reference_rounding_order(m, n, k, bias_dtype):
                                             bias=bias), y)
     layer.bias.mul_(2)                                                 # in-place change is picked up
     assert torch.equal(layer(x), plain + (bias * 2).to(torch.float16))
+
+
+def test_per_token_fast_path_follows_state_changes():
+    """The forward fast path (metadata checks skipped while the state is untouched) still follows
+    in-place updates of the state and rejects bad inputs with the reference's errors."""
+    g = torch.Generator().manual_seed(77)
+    a = ops.QuantizedLinear.from_float((torch.randn(4096, 1024, generator=g) * 0.02).half().cuda())
+    x = torch.randn(8, 1024, generator=g).half().cuda()
+    y0 = a(x).clone()
+    for _ in range(3):
+        y1 = a(x)
+    assert torch.equal(y0, y1) and _native.status() == 0
+    with pytest.raises(ValueError):
+        a(x.float())                                   # not the CUDA FP16 case: full checks, reference's error
+    with pytest.raises(ValueError):
+        a(x[:, :512])
+    a.scales.mul_(2)                                   # version counter changes: image rebuilt, checks repeated
+    y2 = a(x)
+    big = y0.abs() >= 2.0 ** -13
+    assert torch.equal(y2[big], (y0 * 2)[big])
+    a.backend = "gemv"                                 # attribute reassigned: the M == 1 rule applies again
+    with pytest.raises(ValueError, match="M=1"):
+        a(x)
+    a.backend = "auto"
+    assert torch.equal(a(x), y2)
