@@ -81,6 +81,32 @@ def measured_hbm_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense tensor roofline for the prefill rows: the measured cuBLAS bf16 burst (a kernel timed
+    alone), else the profiling recipe's fallback."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            return float(json.loads(path.read_text())["bf16_tflops"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return 1590.0, "fallback"
+
+
+def prefill_roofline(detail):
+    """Tensor-bound roofline of the GEMM kernel from the per-shape table: the largest prefill
+    problem measured (flops = 2*M*N*K per launch / CUDA-event time of the launch)."""
+    rows = [r for rows in (detail or {}).values() for r in rows if r["M"] >= 512 and r["kernel"] == "b200_tcgen05"]
+    if not rows:
+        return None
+    top = max(rows, key=lambda r: r["M"] * r["N"] * r["K"])
+    peak, kind = measured_tensor_peak()
+    return {"bound": "tensor", "achieved": top["TFLOPS"], "peak": peak, "unit": "TFLOP/s",
+            "frac": round(top["TFLOPS"] / peak, 4), "traffic": None, "peak_kind": kind,
+            "kernel": "w4a16_gemm_pair_kernel", "problem": f"{top['N']}x{top['K']}, M={top['M']}",
+            "all_prefill_rows_frac": {f"{r['proj']} {r['N']}x{r['K']} M={r['M']}": round(r["TFLOPS"] / peak, 3) for r in rows}}
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -350,6 +376,7 @@ def run_gpu(args, rank, world, local_rank):
                               "how": "the same step with one eager Python call per linear"}},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks.summary(),
+            "roofline_prefill": prefill_roofline(detail),
             "detail": detail,
         }
         print(json.dumps(result))
