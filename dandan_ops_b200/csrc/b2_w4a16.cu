@@ -288,6 +288,15 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// B2_ROUTE_AUTO hands a batch to the tensor-memory GEMM above 64 rows, and already above 32 rows on
+// layers of at least 4096 native blocks (~10 MB): measured on the 8B/70B projections the pair
+// kernel takes 50 / 87 / 160 us for any M in 33..192 where the streaming kernel needs 63 / 126 /
+// 224 us at M = 48 (its cost grows with every 8 rows of x); at M = 32 the streaming kernel is
+// still ahead (43 / 80 / 141 us), and on small layers the two are within 15 % of each other.
+bool gemm_preferred(int64_t m, const b2::Dims& d) {
+    return m > B2_STREAM_MAX_M || (m > 32 && int64_t(d.n16) * d.kb >= 4096);
+}
+
 bool gemm_applicable(const void* x, int64_t ldx, const b2::Dims& d) {
     return reinterpret_cast<uintptr_t>(x) % 16 == 0 && ldx % 8 == 0 && d.k % 8 == 0;
 }
@@ -409,7 +418,7 @@ inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms, bool pairs_ok
     GemmShape best = kGemmShapes[1];
     int64_t best_cost = INT64_MAX;
     for (int i = 0; i < 5; ++i) {
-        if (forced ? i != forced - 1 : (m <= 128 && i != 0)) continue;
+        if (forced && i != forced - 1) continue;
         if (!pairs_ok && kGemmShapes[i].pair_mt) continue;
         GemmShape g = kGemmShapes[i];
         const int smax = max_splits(g, m, n, kb);
@@ -560,7 +569,7 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
     if (device_info(dev) != B2_OK) dev.sm_count = 148;   // planning also works without a device
     const b2::Dims d = b2::make_dims(n, k);
     const StreamPlan p = plan_stream(m > 0 ? m : 1, d, dev.sm_count);
-    if (m > B2_STREAM_MAX_M && d.k % 8 == 0) {     // assuming an aligned x, as execution_info cannot see the pointer
+    if (gemm_preferred(m, d) && d.k % 8 == 0) {    // assuming an aligned x, as execution_info cannot see the pointer
         const GemmShape shape = gemm_shape(m, d.n, d.kb, dev.sm_count > 0 ? dev.sm_count : 148);
         if (route) *route = B2_ROUTE_TCGEN05;
         if (k_splits) *k_splits = shape.splits;
@@ -598,7 +607,7 @@ int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (device_info(dev) != B2_OK) dev.sm_count = 148;
     const b2::Dims d = b2::make_dims(n, k);
     int64_t need = stream_workspace_bytes(m > 0 ? m : 1, d, dev.sm_count);
-    if (m > B2_STREAM_MAX_M)      // room for the partial tiles of a K-split tensor-memory GEMM
+    if (gemm_preferred(m, d))     // room for the partial tiles of a K-split tensor-memory GEMM
         need = std::max(need, B2_W4A16_TICKET_BYTES + gemm_shape(m, d.n, d.kb, dev.sm_count > 0 ? dev.sm_count : 148).partial_bytes(m, d.n));
     return need;
 }
@@ -700,7 +709,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
     const b2::Dims d = b2::make_dims(n, k);
     if (route == B2_ROUTE_AUTO)
         route = tile_applicable(m, d) ? B2_ROUTE_TILE
-              : (m > B2_STREAM_MAX_M && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
+              : (gemm_preferred(m, d) && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
     if (act && route == B2_ROUTE_TCGEN05) return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue runs in the decode kernels only");
     if (route == B2_ROUTE_TILE) {
         if (!tile_applicable(m, d))

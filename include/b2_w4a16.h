@@ -38,7 +38,7 @@ extern "C" {
 
 /* Kernel families selectable through b2_w4a16_linear_route(). */
 #define B2_ROUTE_AUTO 0      /* by size: tile kernel for M <= 16 on layers up to ~10 MB, streaming kernel up to
-                                B2_STREAM_MAX_M rows, tensor-memory GEMM above */
+                                B2_STREAM_MAX_M rows (32 rows on layers above ~10 MB), tensor-memory GEMM above */
 #define B2_ROUTE_STREAM 1    /* persistent weight-streaming kernel (any M, re-reads the weights every 64 rows) */
 #define B2_ROUTE_TCGEN05 2   /* TMA + tcgen05 GEMM with in-kernel INT4->FP16 converter */
 #define B2_ROUTE_TILE 3      /* one CTA per 16-row tile, whole K in flight at once (M <= 16, K up to ~7k) */
