@@ -323,7 +323,7 @@ def run_gpu(args, rank, world, local_rank):
     if rank == 0 and not args.no_detail:
         detail = {args.workload: per_shape_detail(spec, layers, x_dev, stream, device)}
         if world == 1 and not args.workload_only:
-            # the other BASELINE configurations, one table each (decode GB/s and prefill TFLOP/s)
+            # the other benchmark configurations, one table each (decode GB/s and prefill TFLOP/s)
             for other in sorted(WORKLOADS):
                 if other == args.workload:
                     continue

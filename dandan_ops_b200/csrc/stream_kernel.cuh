@@ -49,7 +49,7 @@ namespace b2 {
 #define B2_STREAM_CTAS16 1
 #endif
 constexpr int kStages = B2_STREAM_STAGES;    // ring depth per warp
-// Shared-memory budget of a CTA with W warps (W = 16: one CTA per SM; W = 4: four per SM,
+// Shared-memory footprint of a CTA with W warps (W = 16: one CTA per SM; W = 4: four per SM,
 // for layers with too few steps to feed 16-warp CTAs on every SM).
 __host__ __device__ constexpr int stream_bar_bytes(int w) { return w * kStages * 8; }
 __host__ __device__ constexpr int stream_ring_bytes(int w) { return w * kStages * kBlockBytes; }
