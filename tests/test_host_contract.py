@@ -207,3 +207,17 @@ def test_ops_namespace_checks_run_before_any_device_work():
     assert torch.ops.dandan_ops.w4a16_contract_version() == 2
     with pytest.raises((RuntimeError, NotImplementedError)):
         torch.ops.dandan_ops.w4a16_gemv(x, layer.packed_weight, layer.scales, layer.zeros, 64)
+
+
+def test_gemm_cost_model_picks_pair_kernels():
+    """Shapes on which the measured cost model prefers each family."""
+    assert _native.plan(512, 12288, 4096)["grid"] == 2 * 48 * 3         # pair, 192 rows of x per pair
+    assert _native.plan(2048, 4096, 4096)["grid"] == 2 * 16 * 8         # pair, 256 rows of x per pair
+    assert _native.plan(256, 24576, 4096)["grid"] == 128                # single CTA, 256 x 192
+    small = _native.plan(100, 4096, 4096)                               # 16 tiles of one row: K split four ways
+    assert small["route"] == "b200_tcgen05" and small["k_splits"] == 4 and small["grid"] == 2 * 16 * 4
+    assert _native.plan(48, 57344, 8192)["route"] == "b200_tcgen05"     # large layer: the GEMM from 33 rows on
+    assert _native.plan(32, 57344, 8192)["route"] == "b200_stream"
+    assert _native.plan(48, 6144, 1024)["route"] == "b200_stream"       # small layer: streaming kernel up to 64 rows
+    split = _native.plan(256, 4096, 28672)                              # 16 tiles, 112 blocks of K: four CTAs per tile
+    assert split["k_splits"] == 4 and split["grid"] == 2 * 16 * 4
