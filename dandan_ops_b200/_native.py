@@ -39,6 +39,7 @@ _SIGNATURES = {
     "b2_w4a16_linear_route": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_linear_bias": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_linear_silu_mul": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_silu_mul_is_fused": (_int, [_i64, _i64, _i64]),
     "b2_w4a16_silu_mul_pairs": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b2_w4a16_rmsnorm_linear": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
                                        _i64, _i64, _i64, _vp, _i64, _vp]),
@@ -237,8 +238,8 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
 
 def linear_silu_mul(x, image, n, k, bias=None, out=None):
     """Fused gate/up projection on a pair-ordered image: [M, K] -> [M, N/2] (see include/b2_w4a16.h).
-    M <= 64 runs the epilogue inside the decode kernels; larger batches run the GEMM and then the
-    elementwise pair kernel."""
+    The epilogue runs inside the decode kernels and the pair GEMM; the few problems that take a
+    single-CTA GEMM tile run the projection and then the elementwise pair kernel."""
     lib = load()
     m = x.shape[0]
     device = x.device
@@ -247,7 +248,8 @@ def linear_silu_mul(x, image, n, k, bias=None, out=None):
         return y
     with torch.cuda.device(device):
         stream = _stream()
-        if m > STREAM_MAX_M:
+        aligned = x.data_ptr() % 16 == 0 and (m == 1 or x.stride(0) % 8 == 0)
+        if not lib.b2_w4a16_silu_mul_is_fused(m, n, k) or (m > STREAM_MAX_M and not aligned and k % 8 == 0):
             full = linear(x, image, n, k, bias=bias)
             _check(lib.b2_w4a16_silu_mul_pairs(full.data_ptr(), full.stride(0), y.data_ptr(), y.stride(0), m, n, stream))
             return y

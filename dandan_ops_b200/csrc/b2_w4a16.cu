@@ -433,17 +433,25 @@ inline GemmShape gemm_shape(int64_t m, int64_t n, int kb, int sms, bool pairs_ok
     return best;
 }
 
+// Shape the GEMM would take for this call (workspace permitting the K-split).
+GemmShape gemm_shape_for_call(int64_t m, const b2::Dims& d, int sms, int64_t workspace_bytes) {
+    GemmShape shape = gemm_shape(m, d.n, d.kb, sms, pair_available());
+    if (B2_W4A16_TICKET_BYTES + shape.partial_bytes(m, d.n) > workspace_bytes) shape.splits = 1;   // no room: one CTA per tile
+    return shape;
+}
+
 int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
-             const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s, int sms, const void* bias) {
+             const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s, int sms, const void* bias,
+             int act = 0) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return fail(B2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
     if (workspace == nullptr) return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(d.k), cuuint64_t(m)};
     const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
-    GemmShape shape = gemm_shape(m, d.n, d.kb, sms, pair_available());
-    if (B2_W4A16_TICKET_BYTES + shape.partial_bytes(m, d.n) > workspace_bytes) shape.splits = 1;   // no room: one CTA per tile
+    const GemmShape shape = gemm_shape_for_call(m, d, sms, workspace_bytes);
     const int pair_mt = shape.pair_mt;
+    if (act && !pair_mt) return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue of the GEMM exists in the pair kernel only");
     const cuuint32_t box[2] = {cuuint32_t(b2::kGemmBK), pair_mt ? cuuint32_t(pair_mt / 2) : 128u};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
@@ -460,6 +468,7 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.tickets = static_cast<unsigned*>(workspace);
     a.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + B2_W4A16_TICKET_BYTES);
     a.splits = shape.splits;
+    a.act = act;
     const bool vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0 && d.n % 8 == 0;
     if (pair_mt) {
         const dim3 pgrid(2 * unsigned((d.n + 255) / 256), unsigned((m + pair_mt - 1) / pair_mt), unsigned(shape.splits));
@@ -467,9 +476,10 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
         const bool tma_y = reinterpret_cast<uintptr_t>(y) % 16 == 0 && ldy % 8 == 0;
         CUtensorMap ymap = map;
         if (tma_y) {
-            const cuuint64_t ydims[2] = {cuuint64_t(d.n), cuuint64_t(m)};
+            // act: the output has n/2 columns and a warp's 32 weight rows give 16 of them
+            const cuuint64_t ydims[2] = {cuuint64_t(act ? d.n / 2 : d.n), cuuint64_t(m)};
             const cuuint64_t ystrides[1] = {cuuint64_t(ldy) * 2};
-            const cuuint32_t ybox[2] = {32, cuuint32_t(pair_mt / 2)};
+            const cuuint32_t ybox[2] = {act ? 16u : 32u, cuuint32_t(pair_mt / 2)};
             if (encode(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, y, ydims, ystrides, ybox, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
                 return fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled failed for y");
@@ -693,9 +703,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
     if (m == 0) return B2_OK;
     if (!x || !native || !y) return fail(B2_ERR_ARGUMENT, "null pointer");
     if (ldx < k || ldy < (act ? n / 2 : n)) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
-    if (act && (n % 16 != 0 || m > B2_STREAM_MAX_M))
-        return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue needs N % 16 == 0 and M <= 64 "
-                                        "(larger batches: b2_w4a16_linear, then b2_w4a16_silu_mul_pairs)");
+    if (act && n % 16 != 0) return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue needs N % 16 == 0");
     if (m > INT_MAX - 128 || m * k > INT_MAX || m * n > INT_MAX)
         return fail(B2_ERR_RANGE, "W4A16 dimensions exceed the kernel index range");
     if (reinterpret_cast<uintptr_t>(native) % 16) return fail(B2_ERR_ARGUMENT, "native image must be 16-byte aligned");
@@ -710,7 +718,12 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
     if (route == B2_ROUTE_AUTO)
         route = tile_applicable(m, d) ? B2_ROUTE_TILE
               : (gemm_preferred(m, d) && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
-    if (act && route == B2_ROUTE_TCGEN05) return fail(B2_ERR_UNSUPPORTED, "the fused gate/up epilogue runs in the decode kernels only");
+    if (act && route == B2_ROUTE_TCGEN05 && !gemm_shape_for_call(m, d, dev.sm_count, workspace_bytes).pair_mt) {
+        // the single-CTA GEMM has no such epilogue: small batches stream, larger ones take two launches
+        if (m > B2_STREAM_MAX_M)
+            return fail(B2_ERR_UNSUPPORTED, "no fused gate/up epilogue for this problem: run b2_w4a16_linear, then b2_w4a16_silu_mul_pairs");
+        route = B2_ROUTE_STREAM;
+    }
     if (route == B2_ROUTE_TILE) {
         if (!tile_applicable(m, d))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
@@ -725,7 +738,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
         if (workspace_bytes < B2_W4A16_TICKET_BYTES)
             return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
-        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), dev.sm_count, bias);
+        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), dev.sm_count, bias, act);
     }
     return fail(B2_ERR_UNSUPPORTED, "unknown route");
 }
@@ -812,6 +825,16 @@ int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual,
 int b2_w4a16_rmsnorm_is_fused(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || check_dims(n, k) != B2_OK || k % 8 != 0) return 0;
     return norm_fused(m, b2::make_dims(n, k)) ? 1 : 0;
+}
+
+int b2_w4a16_silu_mul_is_fused(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || check_dims(n, k) != B2_OK || n % 16 != 0) return 0;
+    if (m <= B2_STREAM_MAX_M) return 1;                    // decode kernels, or the pair GEMM, or the streaming fallback
+    DeviceInfo dev;
+    if (device_info(dev) != B2_OK) dev.sm_count = 148;
+    const b2::Dims d = b2::make_dims(n, k);
+    if (d.k % 8 != 0) return 1;                            // the streaming kernel in chunks of 64 rows
+    return gemm_shape_for_call(m, d, dev.sm_count > 0 ? dev.sm_count : 148, INT64_MAX).pair_mt != 0 ? 1 : 0;
 }
 
 int b2_w4a16_silu_mul_pairs(const void* y_pairs, int64_t ld_in, void* out, int64_t ld_out, int64_t m, int64_t n,

@@ -67,6 +67,9 @@ struct GemmArgs {
     float* partial;
     unsigned* tickets;
     int splits;
+    // Pair kernel only: 1 = rows g / g+8 of every 16-row weight tile are a gate/up pair and y gets
+    // n/2 columns, y[m][8*tile+g] = silu_mul(gate, up) (as StreamArgs::act).
+    int act;
 };
 
 // ---- tcgen05 / TMA helpers ----------------------------------------------------------------

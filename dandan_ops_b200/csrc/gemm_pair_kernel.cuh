@@ -363,6 +363,51 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
             };
             if (!write_y) {
                 // another CTA adds the partial tiles
+            } else if (a.act) {
+                // Gate/up epilogue.  Lanes l and l ^ 8 hold the gate and the up sum of output column
+                // 8 * (row / 16) + (l & 7); the gate lane finishes x rows 0..15 of a chunk, the up lane
+                // rows 16..31, each after one exchange per row with its partner.
+                const bool is_up = (lane & 8) != 0;
+                const __half bias_other = __shfl_xor_sync(0xffffffffu, bias, 8);
+                const __half bias_g = is_up ? bias_other : bias, bias_u = is_up ? bias : bias_other;
+                const int out_col = (n >> 4) * 8 + (lane & 7);          // column of y (n/2 columns in all)
+                const bool out_ok = (n | 8) < a.n;                      // the tile's up row exists (n % 16 == 0 guarantees it)
+                // staged tile of this warp: [MT/2 rows of y][16 columns] FP16, 32-byte rows
+                uint8_t* stage = x_base + (warp - 2) * ((MT / 2) * 32);
+                const int local_col = (lane >> 4) * 8 + (lane & 7);
+#pragma unroll 1
+                for (int cc = 0; cc < MT / 64; ++cc) {
+                    const int col = half * (MT / 2) + cc * 32;
+                    uint32_t v[32];
+                    load_chunk(cc, v);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const uint32_t mine = is_up ? v[e] : v[e + 16];
+                        const uint32_t theirs = __shfl_xor_sync(0xffffffffu, mine, 8);
+                        const float gate = __uint_as_float(is_up ? theirs : v[e]);
+                        const float up = __uint_as_float(is_up ? v[e + 16] : theirs);
+                        __half g16 = __float2half_rn(gate), u16 = __float2half_rn(up);
+                        if (a.bias) { g16 = __hadd(g16, bias_g); u16 = __hadd(u16, bias_u); }
+                        const __half out = silu_mul(g16, u16);
+                        const int row = cc * 32 + e + (is_up ? 16 : 0);          // row of this warp's half of the tile
+                        if constexpr (TMA_Y) {
+                            reinterpret_cast<__half*>(stage + row * 32)[local_col] = out;
+                        } else {
+                            const int m = m0 + half * (MT / 2) + row;
+                            if (out_ok && m < a.m) a.y[int64_t(m) * a.ldy + out_col] = out;
+                        }
+                    }
+                    (void)col;
+                }
+                if constexpr (TMA_Y) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    const int nw = (n0 + quad * 32) >> 1, mw = m0 + half * (MT / 2);
+                    if (lane == 0 && n0 + quad * 32 < a.n && mw < a.m) {
+                        tma_store_2d(&ymap, smem_u32(stage), nw, mw);          // box 16 columns x MT/2 rows of the [M, n/2] output
+                        tma_store_wait_read();
+                    }
+                }
             } else if constexpr (TMA_Y) {
                 // [MT/2 rows of y][32 columns] FP16, 64-byte rows: the lanes of a warp write one row per store
                 uint8_t* stage = x_base + (warp - 2) * ((MT / 2) * 64);

@@ -160,11 +160,15 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
  * dandan_ops/csrc/elementwise.cu:70-73).  The image must be built from rows in PAIR ORDER: every
  * 16-row tile holds 8 gate rows followed by the 8 up rows of the same output columns
  * (N % 16 == 0), and `bias_fp16` follows the same order.  The product and the activation never
- * leave the SM: the decode kernels hold a gate/up pair in one thread.  M <= B2_STREAM_MAX_M;
- * larger batches call b2_w4a16_linear on the same image and then b2_w4a16_silu_mul_pairs. */
+ * leave the SM: the decode kernels hold a gate/up pair in one thread, the pair GEMM exchanges
+ * the two sums between lanes l and l ^ 8 of its epilogue warps.  b2_w4a16_silu_mul_is_fused() tells
+ * whether a problem runs this way (everything except batches above 64 rows whose GEMM tile shape is a
+ * single-CTA one); the others call b2_w4a16_linear on the same image and then
+ * b2_w4a16_silu_mul_pairs, and this function returns B2_ERR_UNSUPPORTED for them. */
 int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                              int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                              int64_t workspace_bytes, void* stream);
+int b2_w4a16_silu_mul_is_fused(int64_t m, int64_t n, int64_t k);
 
 /* Residual add + RMSNorm in front of a projection (the step before the qkv projection of a decoder
  * layer):  s = fp16(x + residual)  (residual may be NULL: s = x),  xn = fp16(fp16(s * rsqrt(mean(s^2)

@@ -150,8 +150,9 @@ def test_image_cache_hit_equals_repack(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("m", [1, 3, 8, 16, 33, 64, 65, 300])
-@pytest.mark.parametrize("rows,k,bias", [(1536, 1024, False), (3072, 1024, True), (1000, 4096, True), (8, 200, False)])
+@pytest.mark.parametrize("m", [1, 3, 8, 16, 33, 64, 65, 300, 1000])
+@pytest.mark.parametrize("rows,k,bias", [(1536, 1024, False), (3072, 1024, True), (1000, 4096, True), (8, 200, False),
+                                          (12288, 4096, False)])
 def test_gate_up_silu_matches_the_separate_launches(m, rows, k, bias):
     """Fused SiLU(gate)*up against the two projections followed by torch's own FP16 silu and
     multiply on the GPU (the reference's unfused sequence), and against a CPU restatement."""
@@ -162,8 +163,9 @@ def test_gate_up_silu_matches_the_separate_launches(m, rows, k, bias):
     assert got.shape == (m, rows) and _native.status() == 0
     g16, u16 = gate(x), up(x)
     separate = torch.nn.functional.silu(g16) * u16
-    # the two routes may add the K partial sums in a different order: compare within the path's tolerance
-    torch.testing.assert_close(got, separate, atol=2e-3, rtol=4e-3)
+    # the separate layers may add the K partial sums in another order (other routes, other tile shapes):
+    # each sum is within 2e-3 + 2e-3|y| of the other, and the product of two such values within about 1e-2
+    torch.testing.assert_close(got, separate, atol=1e-2, rtol=1e-2)
     # on the same FP16 sums the fused arithmetic is the reference's, bit for bit
     pairs = fused.op(x)
     again = _native.silu_mul_pairs(pairs)
@@ -173,8 +175,8 @@ def test_gate_up_silu_matches_the_separate_launches(m, rows, k, bias):
     mism = (again != want)
     assert float(mism.float().mean()) <= 1e-3           # torch's exp may differ by an ulp before the FP16 rounding
     torch.testing.assert_close(again, want, atol=0, rtol=2e-3)
-    if m <= 64:
-        assert torch.equal(got, again)                   # in-kernel epilogue == elementwise kernel on the same sums
+    assert _native.load().b2_w4a16_silu_mul_is_fused(m, 2 * rows, k) == 1
+    assert torch.equal(got, again)                       # in-kernel epilogue == elementwise kernel on the same sums
     cpu = (torch.nn.functional.silu(gp.cpu().float()).half().float() * upv.cpu().float()).half()
     torch.testing.assert_close(again.cpu(), cpu, atol=0, rtol=2e-3)
 
