@@ -43,7 +43,6 @@ _SIGNATURES = {
     "b2_w4a16_silu_mul_pairs": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b2_w4a16_rmsnorm_linear": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
                                        _i64, _i64, _i64, _vp, _i64, _vp]),
-    "b2_w4a16_rmsnorm_is_fused": (_int, [_i64, _i64, _i64]),
     "b2_w4a16_residual_rms_norm": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b2_w4a16_plan": (_int, [_i64, _i64, _i64, ctypes.POINTER(_int), ctypes.POINTER(_int),
                              ctypes.POINTER(_int), ctypes.POINTER(_int)]),
@@ -289,8 +288,8 @@ def residual_rms_norm(x, residual, weight, eps, want_sum=True):
 
 
 def rmsnorm_linear(x, residual, weight, eps, image, n, k, bias=None, want_sum=True):
-    """y = (RMSNorm(x + residual) * weight) @ W^T (+ bias) and the FP16 sum; one launch when the
-    tile kernel takes the problem, norm kernel + linear otherwise (see include/b2_w4a16.h)."""
+    """y = (RMSNorm(x + residual) * weight) @ W^T (+ bias) and the FP16 sum: the norm kernel, then
+    the projection (see include/b2_w4a16.h)."""
     lib = load()
     m = x.shape[0]
     device = x.device
@@ -299,8 +298,7 @@ def rmsnorm_linear(x, residual, weight, eps, image, n, k, bias=None, want_sum=Tr
     if m == 0:
         return y, summed
     with torch.cuda.device(device):
-        fused = bool(lib.b2_w4a16_rmsnorm_is_fused(m, n, k))
-        scratch = None if fused else torch.empty((m, k), dtype=torch.float16, device=device)
+        scratch = torch.empty((m, k), dtype=torch.float16, device=device)
         ws = workspace(device, int(lib.b2_w4a16_workspace_bytes(m, n, k)))
         _check(lib.b2_w4a16_rmsnorm_linear(x.data_ptr(), x.stride(0), _ptr(residual),
                                            residual.stride(0) if residual is not None else 0, weight.data_ptr(),

@@ -158,8 +158,7 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
     cudaGetDevice(&dev);
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        // + 16 KB: the RMSNorm prologue stages the norm weight (kb * 512 bytes) on top of the tile's own need
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemLimit + 16 * 1024);
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemLimit);
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
@@ -168,24 +167,10 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 
 }
 
-// Residual + RMSNorm in front of a projection (all pointers null: none).
-struct NormArgs {
-    const void* residual = nullptr;
-    const void* weight = nullptr;
-    void* summed = nullptr;
-    int64_t ldr = 0, lds = 0;
-    float eps = 0.0f;
-};
-
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
-             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0,
-             const NormArgs& norm = NormArgs()) {
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0) {
     b2::TileArgs a;
     a.act = act;
-    a.residual = static_cast<const __half*>(norm.residual);
-    a.norm_w = static_cast<const __half*>(norm.weight);
-    a.summed = static_cast<__half*>(norm.summed);
-    a.ldr = norm.ldr; a.lds = norm.lds; a.eps = norm.eps;
     a.x = static_cast<const __half*>(x);
     a.native = static_cast<const uint8_t*>(native);
     a.y = static_cast<__half*>(y);
@@ -195,7 +180,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
     a.warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
     const int mt = rows <= 8 ? 1 : 2;
-    const int smem = b2::tile_smem_bytes(d.kb, mt, a.warps) + (norm.weight ? d.kb * 512 : 0);   // + staged norm weight
+    const int smem = b2::tile_smem_bytes(d.kb, mt, a.warps);
     if (mt == 1) return xvec ? launch_tile_one<1, true>(a, smem, s) : launch_tile_one<1, false>(a, smem, s);
     return xvec ? launch_tile_one<2, true>(a, smem, s) : launch_tile_one<2, false>(a, smem, s);
 }
@@ -637,34 +622,32 @@ __global__ void silu_mul_pairs_kernel(const __half* in, int64_t ld_in, __half* o
     }
 }
 
-// Every CTA of the tile kernel normalizes all rows of x for itself, so the prologue's cost grows
-// with M while the separate norm kernel's does not: measured on 4096 x 1024, the fused form wins
-// up to 8 rows (4.6 vs 5.5 us at M = 1, 5.9 vs 6.8 at M = 8) and loses at 16 (8.9 vs 7.2).
-bool norm_fused(int64_t m, const b2::Dims& d) { return m <= 8 && tile_applicable(m, d); }
-
-// Standalone residual + RMSNorm: one warp per row, the same arithmetic and summation order as the
-// tile kernel's prologue.  `summed` may alias nothing else; when null the sums pass through `out`.
-__global__ void residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, int64_t ldr,
-                                         const __half* weight, float eps, __half* summed, int64_t lds,
-                                         __half* out, int64_t ldo, int m, int k) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= m) return;
+// Residual + RMSNorm: one CTA of eight warps per row.  The sum of squares is added in eight
+// lane-strided slices (one per warp), butterfly inside a slice, slices in order: a fixed order, so
+// results do not depend on the launch.  `summed` may alias nothing else; when null the sums pass
+// through `out`.
+__global__ void __launch_bounds__(32 * b2::kNormSlices)
+residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, int64_t ldr,
+                         const __half* weight, float eps, __half* summed, int64_t lds,
+                         __half* out, int64_t ldo, int m, int k) {
+    __shared__ float slice[b2::kNormSlices];
+    __shared__ float inverse_shared;
+    const int row = blockIdx.x;
     const int pieces = k >> 3;
     __half* sums = summed ? summed + row * lds : out + row * ldo;
+    constexpr int kStride = 32 * b2::kNormSlices, kBatch = 4;      // loads in flight per thread; the sum keeps the order of the pieces
     float sq = 0.0f;
-    constexpr int kBatch = 8;               // loads in flight per lane; the sum keeps the order of the pieces
-    for (int c0 = lane; c0 < pieces; c0 += 32 * kBatch) {
+    for (int c0 = threadIdx.x; c0 < pieces; c0 += kStride * kBatch) {
         uint4 v[kBatch], r[kBatch];
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + 32 * j;
+            const int cc = c0 + kStride * j;
             v[j] = cc < pieces ? __ldg(reinterpret_cast<const uint4*>(x + row * ldx + cc * 8)) : make_uint4(0, 0, 0, 0);
             r[j] = (cc < pieces && residual) ? __ldg(reinterpret_cast<const uint4*>(residual + row * ldr + cc * 8)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + 32 * j;
+            const int cc = c0 + kStride * j;
             if (cc < pieces) {
                 if (residual) v[j] = b2::add_piece(v[j], r[j]);
                 *reinterpret_cast<uint4*>(sums + cc * 8) = v[j];
@@ -672,13 +655,22 @@ __global__ void residual_rms_norm_kernel(const __half* x, int64_t ldx, const __h
             }
         }
     }
-    const float inverse = b2::inverse_rms(b2::warp_sum(sq), k, eps);
-    __syncwarp();
-    for (int c0 = lane; c0 < pieces; c0 += 32 * kBatch) {      // every lane re-reads only what it wrote itself
+    sq = b2::warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) slice[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+#pragma unroll
+        for (int p = 0; p < b2::kNormSlices; ++p) total += slice[p];
+        inverse_shared = b2::inverse_rms(total, k, eps);
+    }
+    __syncthreads();
+    const float inverse = inverse_shared;
+    for (int c0 = threadIdx.x; c0 < pieces; c0 += kStride * kBatch) {      // every thread re-reads only what it wrote itself
         uint4 v[kBatch], w[kBatch];
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + 32 * j;
+            const int cc = c0 + kStride * j;
             if (cc < pieces) {
                 v[j] = *reinterpret_cast<const uint4*>(sums + cc * 8);
                 w[j] = __ldg(reinterpret_cast<const uint4*>(weight + cc * 8));
@@ -686,10 +678,11 @@ __global__ void residual_rms_norm_kernel(const __half* x, int64_t ldx, const __h
         }
 #pragma unroll
         for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + 32 * j;
+            const int cc = c0 + kStride * j;
             if (cc < pieces) *reinterpret_cast<uint4*>(out + row * ldo + cc * 8) = b2::norm_piece(v[j], inverse, w[j]);
         }
     }
+    (void)m;
 }
 
 // act = 1: rows g / g+8 of every 16-row tile are a gate/up pair and y gets n/2 columns.
@@ -781,18 +774,8 @@ int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, in
     if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     const b2::Dims d = b2::make_dims(n, k);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (norm_fused(m, d)) {              // fused: the tile kernel normalizes its staged copy of x
-        if (bias_fp16 && reinterpret_cast<uintptr_t>(bias_fp16) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
-        if (reinterpret_cast<uintptr_t>(native) % 16) return fail(B2_ERR_ARGUMENT, "native image must be 16-byte aligned");
-        if (ldy < n) return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
-        NormArgs norm;
-        norm.residual = residual; norm.weight = norm_weight; norm.summed = summed;
-        norm.ldr = ldr; norm.lds = lds; norm.eps = eps;
-        return run_tile(x, ldx, native, y, ldy, m, d, workspace, true, s, bias_fp16, 0, norm);
-    }
-    if (!xn_scratch) return fail(B2_ERR_ARGUMENT, "this problem runs the norm as its own kernel and needs xn_scratch [M, K]");
-    const int warps = 8;
-    residual_rms_norm_kernel<<<unsigned((m + warps - 1) / warps), warps * 32, 0, s>>>(
+    if (!xn_scratch) return fail(B2_ERR_ARGUMENT, "xn_scratch [M, K] is required");
+    residual_rms_norm_kernel<<<unsigned(m), 32 * b2::kNormSlices, 0, s>>>(
         static_cast<const __half*>(x), ldx, static_cast<const __half*>(residual), ldr,
         static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
         static_cast<__half*>(xn_scratch), k, int(m), int(k));
@@ -814,17 +797,11 @@ int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual,
     if (ldx < k || ldo < k || (residual && ldr < k) || (summed && lds < k))
         return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
     if (m > INT_MAX - 128 || k > INT_MAX - 64 || m * k > INT_MAX) return fail(B2_ERR_RANGE, "dimensions exceed the kernel index range");
-    const int warps = 8;
-    residual_rms_norm_kernel<<<unsigned((m + warps - 1) / warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+    residual_rms_norm_kernel<<<unsigned(m), 32 * b2::kNormSlices, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(x), ldx, static_cast<const __half*>(residual), ldr,
         static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
         static_cast<__half*>(out), ldo, int(m), int(k));
     return after_launch("residual_rms_norm_kernel");
-}
-
-int b2_w4a16_rmsnorm_is_fused(int64_t m, int64_t n, int64_t k) {
-    if (m <= 0 || check_dims(n, k) != B2_OK || k % 8 != 0) return 0;
-    return norm_fused(m, b2::make_dims(n, k)) ? 1 : 0;
 }
 
 int b2_w4a16_silu_mul_is_fused(int64_t m, int64_t n, int64_t k) {

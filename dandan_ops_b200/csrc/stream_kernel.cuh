@@ -172,6 +172,7 @@ __device__ __forceinline__ uint4 norm_piece(const uint4& v, float inverse, const
     }
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
+constexpr int kNormSlices = 8;       // a row's sum of squares is added in eight lane-strided slices
 // Sum over a warp in a fixed order (the same in the fused prologue and in the standalone kernel).
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

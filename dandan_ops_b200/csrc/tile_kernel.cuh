@@ -32,14 +32,6 @@ struct TileArgs {
     int n16, kb;
     int warps;              // warps per CTA = min(16, 2*kb)
     int act;                // as StreamArgs::act
-    // RMSNorm prologue (norm_w != null; needs the vectorised x path): the CTA multiplies by
-    // RMSNorm(x + residual) * norm_w instead of x.  residual may be null; CTA 0 stores the FP16
-    // sum to `summed` if that is not null.
-    const __half* residual;
-    const __half* norm_w;
-    __half* summed;
-    int64_t ldr, lds;
-    float eps;
 };
 
 __host__ __device__ constexpr int tile_smem_bytes(int kb, int mt, int warps) {
@@ -74,40 +66,7 @@ w4a16_tile_kernel(const TileArgs a) {
         }
     }
     // stage x for all columns (zero beyond M and K)
-    const bool norm = XVEC && a.norm_w != nullptr;
-    // RMSNorm weight, staged behind the reduction tiles (the launch adds kb * 512 bytes for it)
-    uint4* nw = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(red) + a.warps * MT * 512);
-    if (norm) {
-        // x + residual (rounded to FP16) and the norm weight: every global load of the prologue is
-        // issued here, next to the weight copies, so that the passes below only touch shared memory
-        const int pieces_per_row = a.kb * 32;
-        const int total = MP * pieces_per_row;
-        constexpr int kBatch = 4;            // pieces per thread whose loads are in flight together
-        for (int i0 = threadIdx.x; i0 < total; i0 += kBatch * blockDim.x) {
-            uint4 xv[kBatch], rv[kBatch];
-#pragma unroll
-            for (int j = 0; j < kBatch; ++j) {
-                const int i = i0 + j * blockDim.x;
-                const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
-                const bool inside = i < total && m < a.m && cc * 8 < a.k;
-                xv[j] = inside ? __ldg(reinterpret_cast<const uint4*>(a.x + int64_t(m) * a.ldx + cc * 8)) : make_uint4(0, 0, 0, 0);
-                rv[j] = inside && a.residual ? __ldg(reinterpret_cast<const uint4*>(a.residual + int64_t(m) * a.ldr + cc * 8))
-                                             : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int j = 0; j < kBatch; ++j) {
-                const int i = i0 + j * blockDim.x;
-                if (i >= total) break;
-                const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
-                const uint4 v = a.residual ? add_piece(xv[j], rv[j]) : xv[j];       // zeros stay zeros outside
-                if (a.summed && blockIdx.x == 0 && m < a.m && cc * 8 < a.k)
-                    *reinterpret_cast<uint4*>(a.summed + int64_t(m) * a.lds + cc * 8) = v;
-                *reinterpret_cast<uint4*>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16) = v;
-            }
-        }
-        for (int cc = threadIdx.x; cc < pieces_per_row; cc += blockDim.x)
-            nw[cc] = cc * 8 < a.k ? __ldg(reinterpret_cast<const uint4*>(a.norm_w + cc * 8)) : make_uint4(0, 0, 0, 0);
-    } else {
+    {
         const int pieces_per_row = a.kb * 32;
         const int total = MP * pieces_per_row;
         for (int i = threadIdx.x; i < total; i += blockDim.x) {
@@ -115,24 +74,6 @@ w4a16_tile_kernel(const TileArgs a) {
             const int k = cc * 8;
             stage_piece<XVEC, false>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16, a.x + int64_t(m) * a.ldx + k,
                               m < a.m && k < a.k, k, a.k);
-        }
-    }
-    if (norm) {
-        const int pieces_per_row = a.kb * 32;
-        const int total = MP * pieces_per_row;
-        auto piece_at = [&](int m, int cc) { return reinterpret_cast<uint4*>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16); };
-        __syncthreads();
-        float* inverse = reinterpret_cast<float*>(red);            // the reduction tiles are not in use yet
-        for (int m = warp; m < a.m; m += a.warps) {
-            float sq = 0.0f;
-            for (int cc = lane; cc < pieces_per_row; cc += 32) sq = sumsq_piece(*piece_at(m, cc), sq);   // zeros beyond K
-            sq = warp_sum(sq);
-            if (lane == 0) inverse[m] = inverse_rms(sq, a.k, a.eps);
-        }
-        __syncthreads();
-        for (int i = threadIdx.x; i < total; i += blockDim.x) {
-            const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
-            if (m < a.m) *piece_at(m, cc) = norm_piece(*piece_at(m, cc), inverse[m], nw[cc]);
         }
     }
     __syncthreads();        // x staged; barrier initialisation visible to every waiter

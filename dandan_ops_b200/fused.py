@@ -142,10 +142,9 @@ class GateUpSilu(nn.Module):
 class RmsNormLinear(nn.Module):
     """`forward(x, residual=None) -> (y, summed)`: residual add + RMSNorm + projection.
 
-    The step in front of the qkv projection of a decoder layer (the reference runs
-    `residual_rms_norm` as its own kernel, dandan_ops/elementwise.py:156-165).  For decode batches
-    on small layers the projection kernel normalizes its own staged copy of x - one launch; other
-    sizes run a norm kernel with the same arithmetic and then the projection."""
+    The step in front of the qkv projection of a decoder layer, with the rounding order of the
+    reference's `residual_rms_norm` (dandan_ops/elementwise.py:156-165): one norm kernel (a CTA per
+    row, fixed summation order) and the projection, both on the current stream."""
 
     def __init__(self, norm_weight, layer, eps=1e-5):
         super().__init__()

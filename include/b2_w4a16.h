@@ -174,19 +174,17 @@ int b2_w4a16_silu_mul_is_fused(int64_t m, int64_t n, int64_t k);
  * layer):  s = fp16(x + residual)  (residual may be NULL: s = x),  xn = fp16(fp16(s * rsqrt(mean(s^2)
  * + eps)) * norm_weight),  y = xn @ W^T (+ bias) - the rounding order of the reference's
  * `residual_rms_norm` (dandan_ops/elementwise.py:156-165, dandan_ops/csrc/elementwise.cu:39-62).
- * `summed` (optional, [M, K], row stride lds) receives s for the residual stream.
- * For problems the tile kernel takes (b2_w4a16_rmsnorm_is_fused() == 1: M <= 8, small layers) the
- * kernel normalizes its own shared-memory copy of x while the weight copies are in flight and no
- * extra launch happens; otherwise the norm runs as one kernel into `xn_scratch` ([M, K] FP16,
- * row stride K, required then) followed by b2_w4a16_linear.  Both paths use the same arithmetic
- * and summation order.  K, ldx, ldr, lds multiples of 8; pointers 16-byte aligned. */
+ * `summed` (optional, [M, K], row stride lds) receives s for the residual stream; `xn_scratch`
+ * ([M, K] FP16, row stride K) receives xn.  Two launches on `stream`: the norm kernel below, then
+ * b2_w4a16_linear.  (A variant that normalized the tile kernel's shared-memory copy of x inside the
+ * projection launch was measured and dropped: every CTA repeats the norm, which cost more than the
+ * second launch.)  K, ldx, ldr, lds multiples of 8; pointers 16-byte aligned. */
 int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, int64_t ldr, const void* norm_weight,
                             float eps, void* summed, int64_t lds, void* xn_scratch, const void* native,
                             const void* bias_fp16, void* y, int64_t ldy, int64_t m, int64_t n, int64_t k,
                             void* workspace, int64_t workspace_bytes, void* stream);
-int b2_w4a16_rmsnorm_is_fused(int64_t m, int64_t n, int64_t k);
 
-/* The norm alone (the kernel the unfused path of b2_w4a16_rmsnorm_linear launches):
+/* The norm alone (the first launch of b2_w4a16_rmsnorm_linear):
  * summed = fp16(x + residual) (optional output), out = RMSNorm(summed) * norm_weight. */
 int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual, int64_t ldr, const void* norm_weight,
                                float eps, void* summed, int64_t lds, void* out, int64_t ldo, int64_t m, int64_t k,
