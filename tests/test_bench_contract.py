@@ -1,0 +1,48 @@
+"""The benchmark's reference arm runs on host cores only, so its output contract is checked here;
+the GPU arm's JSON line is produced by the same code path and checked for the shared keys when a
+GPU is present."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+SHARED = {"metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+          "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"}
+
+
+def _last_json(stdout):
+    lines = [l for l in stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1, stdout
+    return json.loads(lines[0])
+
+
+def test_reference_arm_prints_one_contract_line():
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                          capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr
+    line = _last_json(proc.stdout)
+    assert SHARED <= set(line) and line["impl"] == "reference"
+    assert line["metric"] == "w4a16_decode_weight_hbm_GBps" and line["unit"] == "GB/s" and line["higher_is_better"] is True
+    assert line["value"] > 0 and line["config"]["workload"] == "qwen3-0.6b-decode" and line["vs_baseline"] is None
+    cpu = line["cpu_baseline"]
+    assert cpu["kind"] == "port" and cpu["cores"] >= 1 and cpu["value"] == line["value"] and cpu["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+@pytest.mark.gpu
+def test_gpu_arm_prints_one_contract_line():
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--steps", "2", "--warmup", "3", "--no-cpu", "--workload-only"],
+                          capture_output=True, text=True, timeout=900, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = _last_json(proc.stdout)
+    assert SHARED | {"roofline", "gpu_launches", "clocks", "roofline_prefill"} <= set(line)
+    roof = line["roofline"]
+    assert roof["bound"] == "hbm" and 0 < roof["frac"] < 1.2 and roof["unit"] == "GB/s" and roof["traffic"] > 0
+    assert line["gpu_launches"] == 2 * 448 and line["n_gpus"] == 1 and line["dtype"] == "f16"
+    e2e = line["e2e"]
+    assert e2e["value"] > 0 and e2e["h2d_bytes_per_step"] > 0 and e2e["d2h_bytes_per_step"] > 0 and e2e["eager"]["value"] > 0
+    pre = line["roofline_prefill"]
+    assert pre["bound"] == "tensor" and pre["unit"] == "TFLOP/s" and 0 < pre["frac"] < 1.2
