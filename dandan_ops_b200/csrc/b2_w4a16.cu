@@ -141,18 +141,21 @@ int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaS
 // Latency-oriented tile kernel: whole K of one row tile per CTA (small and mid-size layers).
 // ---------------------------------------------------------------------------------------
 constexpr int kTileSmemLimit = 200 * 1024;
-constexpr int64_t kTileMaxBlocks = 4096;       // native blocks (9.6 MB of image); larger layers stream
+constexpr int64_t kTileMaxBlocks = 4096;       // native blocks (9.6 MB of image) at 5..16 rows of x; larger layers stream
 
 bool tile_applicable(int64_t rows, const b2::Dims& d) {
     if (rows > 16) return false;
-    const int mt = rows <= 8 ? 1 : 2;
     const int warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
-    return int64_t(d.n16) * d.kb <= kTileMaxBlocks && b2::tile_smem_bytes(d.kb, mt, warps) <= kTileSmemLimit;
+    // Native blocks up to which one CTA per row tile beats the persistent streaming kernel (measured on
+    // N x 4096 and 4096 x 8192 layers): the fewer rows of x, the less shared memory a CTA stages and the
+    // more CTAs share an SM.
+    const int64_t limit = rows == 1 ? 2 * kTileMaxBlocks : rows <= 4 ? 3 * kTileMaxBlocks / 2 : kTileMaxBlocks;
+    return int64_t(d.n16) * d.kb <= limit && b2::tile_smem_bytes(d.kb, int(rows), warps) <= kTileSmemLimit;
 }
 
-template <int MT, bool XVEC>
+template <int MT, bool XVEC, bool FULL>
 int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
-    auto kernel = b2::w4a16_tile_kernel<MT, XVEC>;
+    auto kernel = b2::w4a16_tile_kernel<MT, XVEC, FULL>;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -168,7 +171,7 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 }
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
-             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0) {
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0, int sms = 148) {
     b2::TileArgs a;
     a.act = act;
     a.x = static_cast<const __half*>(x);
@@ -180,9 +183,18 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
     a.warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
     const int mt = rows <= 8 ? 1 : 2;
-    const int smem = b2::tile_smem_bytes(d.kb, mt, a.warps);
-    if (mt == 1) return xvec ? launch_tile_one<1, true>(a, smem, s) : launch_tile_one<1, false>(a, smem, s);
-    return xvec ? launch_tile_one<2, true>(a, smem, s) : launch_tile_one<2, false>(a, smem, s);
+    // Stage all mt * 8 rows (zeros beyond M) unless that costs occupancy: the padded layout is the
+    // faster one as long as every CTA of the grid still finds a place in the first wave.
+    const int padded = b2::tile_smem_bytes(d.kb, mt * 8, a.warps);
+    const int per_sm = padded <= kTileSmemLimit ? std::min(227 * 1024 / (padded + 1024), 2048 / (a.warps * 32)) : 0;
+    const bool full = rows == mt * 8 || int64_t(d.n16) <= int64_t(per_sm) * (sms > 0 ? sms : 148);
+    const int smem = b2::tile_smem_bytes(d.kb, full ? mt * 8 : int(rows), a.warps);
+    if (mt == 1) {
+        if (full) return xvec ? launch_tile_one<1, true, true>(a, smem, s) : launch_tile_one<1, false, true>(a, smem, s);
+        return xvec ? launch_tile_one<1, true, false>(a, smem, s) : launch_tile_one<1, false, false>(a, smem, s);
+    }
+    if (full) return xvec ? launch_tile_one<2, true, true>(a, smem, s) : launch_tile_one<2, false, true>(a, smem, s);
+    return xvec ? launch_tile_one<2, true, false>(a, smem, s) : launch_tile_one<2, false, false>(a, smem, s);
 }
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
@@ -721,7 +733,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
         if (!tile_applicable(m, d))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
-        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act);
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count);
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,

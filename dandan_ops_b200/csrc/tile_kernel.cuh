@@ -34,18 +34,23 @@ struct TileArgs {
     int act;                // as StreamArgs::act
 };
 
-__host__ __device__ constexpr int tile_smem_bytes(int kb, int mt, int warps) {
+// `rows` = rows of x that exist (1..16): only those are staged, so that at M = 1 a CTA of a
+// 4096-column layer needs 55 KB instead of 120 KB and four of them share an SM.
+__host__ __device__ constexpr int tile_smem_bytes(int kb, int rows, int warps) {
     // barriers (padded to 128) + blocks + staged x + reduction tiles
-    return ((kb * 8 + 127) / 128) * 128 + kb * kBlockBytes + kb * 4 * stream_x_chunk_bytes(mt * 8) +
-           warps * mt * 512;
+    return ((kb * 8 + 127) / 128) * 128 + kb * kBlockBytes + kb * 4 * stream_x_chunk_bytes(rows) +
+           warps * (rows <= 8 ? 1 : 2) * 512;
 }
 
-template <int MT, bool XVEC>
+// FULL: all MT * 8 rows of x are staged (zeros beyond M): compile-time layout, no row predicates -
+// the faster form whenever the padded rows do not cost occupancy.  Otherwise only the M rows that
+// exist are staged and lanes of missing rows use zero fragments.
+template <int MT, bool XVEC, bool FULL>
 __global__ void __launch_bounds__(kTileMaxWarps * 32)
 w4a16_tile_kernel(const TileArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int MP = MT * 8;
-    constexpr int kChunk = stream_x_chunk_bytes(MP);
+    const int rows = FULL ? MT * 8 : a.m;
+    const int kChunk = stream_x_chunk_bytes(rows);          // `rows` rows of 144 bytes per 64-column chunk
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int nt = blockIdx.x;
@@ -68,7 +73,7 @@ w4a16_tile_kernel(const TileArgs a) {
     // stage x for all columns (zero beyond M and K)
     {
         const int pieces_per_row = a.kb * 32;
-        const int total = MP * pieces_per_row;
+        const int total = rows * pieces_per_row;
         for (int i = threadIdx.x; i < total; i += blockDim.x) {
             const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
             const int k = cc * 8;
@@ -109,8 +114,9 @@ w4a16_tile_kernel(const TileArgs a) {
             const uint32_t wa = pick(ca, i), wb = pick(cb, i);
             uint4 xv[MT];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-                xv[mt] = *reinterpret_cast<const uint4*>(xchunk + mt * (8 * 144) + i * 16);
+            for (int mt = 0; mt < MT; ++mt)      // rows of x that do not exist are not staged: their columns of the product are zero
+                xv[mt] = (FULL || mt * 8 + g < rows) ? *reinterpret_cast<const uint4*>(xchunk + mt * (8 * 144) + i * 16)
+                                                     : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
