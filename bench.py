@@ -30,6 +30,7 @@ P-times wider layer, no exchange); llama3-70b-mlp splits each layer's rows over 
 torch FP32 matmul on all host threads) on a bounded sample of the same workload.
 """
 import argparse
+import copy
 import json
 import os
 import statistics
@@ -387,12 +388,14 @@ def run_gpu(args, rank, world, local_rank):
 
 def per_shape_detail(spec, layers, x_dev, stream, device):
     """Median CUDA-graph replay time of every (projection, M): microseconds, weight GB/s, TFLOPS.
-    Each graph walks all layers of the workload, so consecutive launches never reuse weights
-    (single layers larger than L2 need no rotation).  `detail_ms` adds batch sizes that are not
+    Decode sizes: each graph walks >= 256 MB of distinct layers once, so every launch streams its
+    weights from HBM in every replay.  Prefill sizes: one pass over the column, L2 flushed (a 256 MB
+    memset, untimed) before every replay.  `detail_ms` adds batch sizes that are not
     part of the timed step, among them the prefill sizes that run on the tcgen05 GEMM."""
     out = []
     gen = torch.Generator().manual_seed(spec["seed"] + 6)
     all_ms = sorted(set(spec["ms"]) | set(spec.get("detail_ms", [])))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # larger than L2
     with torch.cuda.stream(stream):
         # Decode sizes of every projection first, the prefill sizes last: seconds of GEMM at the
         # power cap lower the SM clock for a while, which would tax whatever is timed right after.
@@ -402,10 +405,19 @@ def per_shape_detail(spec, layers, x_dev, stream, device):
                 if not column:
                     continue
                 n = column[0][1]
+                if not prefill:
+                    # Decode sizes are timed over >= 256 MB of distinct weights (copies of the column's layers),
+                    # so that a replay streams every layer from HBM, as the step does, instead of finding a
+                    # small column (28 x 2.4 MB) still in L2 from the previous replay.
+                    need = int(256e6 // max(1.0, weight_bytes(n, k))) + 1
+                    base = list(column)
+                    while len(column) < min(need, 160):
+                        name_, n_, k_, layer_ = base[len(column) % len(base)]
+                        column.append((name_, n_, k_, copy.deepcopy(layer_)))
                 for m in all_ms:
                     if (m > 64) != prefill:
                         continue
-                    reps = 1 if prefill else max(1, int(300e6 // max(1.0, len(column) * weight_bytes(n, k))))
+                    reps = 1
                     x = x_dev.get((m, k))
                     if x is None:
                         x = torch.randn(m, k, generator=gen).half().to(device)
@@ -420,6 +432,8 @@ def per_shape_detail(spec, layers, x_dev, stream, device):
                     samples = []
                     for _ in range(7):
                         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        if prefill:
+                            flush.zero_()
                         e0.record(stream)
                         graph.replay()
                         e1.record(stream)
