@@ -18,19 +18,22 @@
 // Roles per CTA (10 warps):
 //   warp 0      copy producer: bulk copies of this CTA's 8 native blocks per 256 columns of K,
 //               TMA loads of this CTA's x rows; the loads of BOTH CTAs complete the leader's
-//               x_full barrier (cp.async.bulk.tensor with .cta_group::2)
+//               full barrier (cp.async.bulk.tensor with .cta_group::2)
 //   warp 1      allocates/frees tensor memory (cta_group::2, both CTAs); in the leader CTA
-//               (cluster rank 0) one lane issues the MMAs and commits to the barriers of both CTAs
-//   warps 2..9  converters: thread = weight row (tensor-memory lane), two warps per lane
-//               quadrant, 32 of the step's 64 columns each; afterwards the epilogue
-//               (tcgen05.ld -> FP16 (+bias) -> y, transposed: a warp stores 32 consecutive
-//               output columns of one row of y per instruction)
+//               (cluster rank 0) one lane issues the MMAs and one commit per step to both CTAs
+//   warps 2..9  converters: thread = weight row (tensor-memory lane); the two warps of a lane
+//               quadrant take alternate 64-column steps (one 32-column tcgen05.st per step and
+//               quadrant); afterwards the epilogue: tcgen05.ld gives a thread 32 rows of y for
+//               ONE column, the warp transposes through the idle x ring and stores its
+//               32 columns x MT/2 rows with one TMA store (2-byte global stores for unaligned y;
+//               lanes l and l ^ 8 exchange sums first when the gate/up epilogue is on)
 //
 // Barriers (every wait is bounded, as in the single-CTA kernel):
 //   raw_full/raw_free[r]   local: bulk copy done / all converter warps finished with raw stage r
-//   x_full[s]              leader only: transaction bytes of both CTAs' x loads
-//   w_full[s]              leader only: one arrival per converter warp of both CTAs
-//   x_free[s], w_free[s]   both CTAs: tcgen05.commit (multicast) after the MMAs that read stage s
+//   full[s % XS]           leader only: transaction bytes of both CTAs' x loads + one arrival per
+//                          converter warp of both CTAs that wrote step s
+//   done[s % XS]           both CTAs: tcgen05.commit (multicast) after the MMAs of step s; frees the
+//                          x stage for the producers and the tensor-memory stage for the converters
 //   acc_full               both CTAs: tcgen05.commit after the last MMA
 //   epi_written, epi_last  local, K-splitting only: the CTA's partial tile is in global memory /
 //                          thread 64 has drawn the tile's ticket
