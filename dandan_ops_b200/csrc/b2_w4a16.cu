@@ -143,15 +143,30 @@ int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaS
 constexpr int kTileSmemLimit = 200 * 1024;
 constexpr int64_t kTileMaxBlocks = 4096;       // native blocks (9.6 MB of image) at 5..16 rows of x; larger layers stream
 
-bool tile_applicable(int64_t rows, const b2::Dims& d) {
+// CTAs per row tile of the tile kernel (a cluster that splits K): the largest of 4 and 2 that leaves
+// every CTA at least 8 half blocks (measured: a 1024 x 2048 layer gains 10 % from two CTAs of 8 warps, a
+// 1024 x 1024 layer loses 15 % from two of 4) and fits all clusters on the device at once; else 1.
+int tile_ksplit(const b2::Dims& d, int sms, bool clusters_ok = true) {
+    if (!clusters_ok) return 1;
+    for (int s = 4; s >= 2; s >>= 1)
+        if (int64_t(s) * d.n16 <= sms && d.kb * 2 >= s * 8) return s;
+    return 1;
+}
+
+bool tile_applicable(int64_t rows, const b2::Dims& d, int split) {
     if (rows > 16) return false;
-    const int warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
+    const int kb_cta = (d.kb + split - 1) / split;
+    const int warps = kb_cta * 2 < b2::kTileMaxWarps ? kb_cta * 2 : b2::kTileMaxWarps;
     // Native blocks up to which one CTA per row tile beats the persistent streaming kernel (measured on
     // N x 4096 and 4096 x 8192 layers): the fewer rows of x, the less shared memory a CTA stages and the
     // more CTAs share an SM.
     const int64_t limit = rows == 1 ? 2 * kTileMaxBlocks : rows <= 4 ? 3 * kTileMaxBlocks / 2 : kTileMaxBlocks;
-    return int64_t(d.n16) * d.kb <= limit && b2::tile_smem_bytes(d.kb, int(rows), warps) <= kTileSmemLimit;
+    const int smem = split > 1 ? b2::tile_smem_bytes(kb_cta, rows <= 8 ? 8 : 16, warps) + split * (rows <= 8 ? 1 : 2) * 512
+                               : b2::tile_smem_bytes(d.kb, int(rows), warps);
+    return int64_t(d.n16) * d.kb <= limit && smem <= kTileSmemLimit;
 }
+
+bool pair_available();
 
 template <int MT, bool XVEC, bool FULL>
 int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
@@ -165,9 +180,24 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
-    kernel<<<a.n16, a.warps * 32, smem, s>>>(a);
-    return after_launch("w4a16_tile_kernel");
-
+    if (a.ksplit == 1) {
+        kernel<<<a.n16, a.warps * 32, smem, s>>>(a);
+        return after_launch("w4a16_tile_kernel");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(a.n16) * unsigned(a.ksplit), 1, 1);
+    cfg.blockDim = dim3(unsigned(a.warps) * 32, 1, 1);
+    cfg.dynamicSmemBytes = size_t(smem);
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = unsigned(a.ksplit); attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, a);
+    if (le != cudaSuccess) return cuda_fail("w4a16_tile_kernel", le);
+    return B2_OK;
 }
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
@@ -181,8 +211,17 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.bias = static_cast<const __half*>(bias);
     a.ldx = ldx; a.ldy = ldy;
     a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
-    a.warps = d.kb * 2 < b2::kTileMaxWarps ? d.kb * 2 : b2::kTileMaxWarps;
     const int mt = rows <= 8 ? 1 : 2;
+    // Two CTAs per row tile (a cluster, K halved) when the tiles leave more than half of the SMs idle and
+    // a CTA's 16 warps would each take more than one unit: the pair finishes in one round instead of two.
+    a.ksplit = tile_ksplit(d, sms > 0 ? sms : 148, pair_available());
+    const int kb_cta = (d.kb + a.ksplit - 1) / a.ksplit;
+    a.warps = kb_cta * 2 < b2::kTileMaxWarps ? kb_cta * 2 : b2::kTileMaxWarps;
+    if (a.ksplit > 1) {
+        const int smem2 = b2::tile_smem_bytes(kb_cta, mt * 8, a.warps) + a.ksplit * mt * 512;      // padded rows: the grid is small
+        if (mt == 1) return xvec ? launch_tile_one<1, true, true>(a, smem2, s) : launch_tile_one<1, false, true>(a, smem2, s);
+        return xvec ? launch_tile_one<2, true, true>(a, smem2, s) : launch_tile_one<2, false, true>(a, smem2, s);
+    }
     // Stage all mt * 8 rows (zeros beyond M) unless that costs occupancy: the padded layout is the
     // faster one as long as every CTA of the grid still finds a place in the first wave.
     const int padded = b2::tile_smem_bytes(d.kb, mt * 8, a.warps);
@@ -584,10 +623,11 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
         if (rows_per_launch) *rows_per_launch = int(m);
         return B2_OK;
     }
-    if (m > 0 && tile_applicable(m, d)) {          // whole K of a row tile per CTA, no split between CTAs
+    const int split = tile_ksplit(d, dev.sm_count > 0 ? dev.sm_count : 148);
+    if (m > 0 && tile_applicable(m, d, split)) {   // whole K of a row tile per CTA, or per cluster of 2 or 4 CTAs
         if (route) *route = B2_ROUTE_TILE;
-        if (k_splits) *k_splits = 1;
-        if (grid) *grid = d.n16;
+        if (k_splits) *k_splits = split;
+        if (grid) *grid = d.n16 * split;
         if (rows_per_launch) *rows_per_launch = int(m);
         return B2_OK;
     }
@@ -720,8 +760,9 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
     if (int rc = device_info(dev)) return rc;
     if (dev.cc_major != 10) return fail(B2_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     const b2::Dims d = b2::make_dims(n, k);
+    const int tile_split = tile_ksplit(d, dev.sm_count, pair_available());
     if (route == B2_ROUTE_AUTO)
-        route = tile_applicable(m, d) ? B2_ROUTE_TILE
+        route = tile_applicable(m, d, tile_split) ? B2_ROUTE_TILE
               : (gemm_preferred(m, d) && gemm_applicable(x, ldx, d)) ? B2_ROUTE_TCGEN05 : B2_ROUTE_STREAM;
     if (act && route == B2_ROUTE_TCGEN05 && !gemm_shape_for_call(m, d, dev.sm_count, workspace_bytes).pair_mt) {
         // the single-CTA GEMM has no such epilogue: small batches stream, larger ones take two launches
@@ -730,7 +771,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
         route = B2_ROUTE_STREAM;
     }
     if (route == B2_ROUTE_TILE) {
-        if (!tile_applicable(m, d))
+        if (!tile_applicable(m, d, tile_split))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
         return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count);

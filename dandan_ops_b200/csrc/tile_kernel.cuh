@@ -32,6 +32,9 @@ struct TileArgs {
     int n16, kb;
     int warps;              // warps per CTA = min(16, 2*kb)
     int act;                // as StreamArgs::act
+    int ksplit;             // 1, 2 or 4: a cluster of that many CTAs shares a row tile, each takes its share
+                            // of the K blocks and the others hand their 16 x 8*MT sums to the first through
+                            // distributed shared memory (layers whose row tiles leave most SMs idle)
 };
 
 // `rows` = rows of x that exist (1..16): only those are staged, so that at M = 1 a CTA of a
@@ -53,30 +56,40 @@ w4a16_tile_kernel(const TileArgs a) {
     const int kChunk = stream_x_chunk_bytes(rows);          // `rows` rows of 144 bytes per 64-column chunk
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int nt = blockIdx.x;
-    const int bar_bytes = ((a.kb * 8 + 127) / 128) * 128;
+    // this CTA's share of the row tile: blocks kb0 .. kb0 + kbn - 1 of K
+    uint32_t part = 0;
+    if (a.ksplit > 1) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(part));
+        // first phase of "both CTAs are running", completed before the hand-over below touches the
+        // other CTA's shared memory
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    }
+    const int nt = blockIdx.x / a.ksplit;
+    const int kb0 = int(part) * a.kb / a.ksplit, kbn = (int(part) + 1) * a.kb / a.ksplit - kb0;
+    const int kb_max = (a.kb + a.ksplit - 1) / a.ksplit;     // both CTAs of a pair use one layout
+    const int bar_bytes = ((kb_max * 8 + 127) / 128) * 128;
     uint8_t* blocks = smem + bar_bytes;
-    uint8_t* xs = blocks + a.kb * kBlockBytes;
-    float4* red = reinterpret_cast<float4*>(xs + a.kb * 4 * kChunk);
+    uint8_t* xs = blocks + kb_max * kBlockBytes;
+    float4* red = reinterpret_cast<float4*>(xs + kb_max * 4 * kChunk);
     const uint32_t bar0 = smem_u32(smem);
 
     if (threadIdx.x == 0) {
-        for (int b = 0; b < a.kb; ++b) mbar_init(bar0 + b * 8, 1);
+        for (int b = 0; b < kbn; ++b) mbar_init(bar0 + b * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        const uint8_t* src = a.native + int64_t(nt) * kBlockBytes;
+        const uint8_t* src = a.native + (int64_t(kb0) * a.n16 + nt) * kBlockBytes;
         const int64_t stride = int64_t(a.n16) * kBlockBytes;
-        for (int b = 0; b < a.kb; ++b) {
+        for (int b = 0; b < kbn; ++b) {
             mbar_expect_tx(bar0 + b * 8, kBlockBytes);
             bulk_copy_g2s(smem_u32(blocks + b * kBlockBytes), src + b * stride, kBlockBytes, bar0 + b * 8);
         }
     }
     // stage x for all columns (zero beyond M and K)
     {
-        const int pieces_per_row = a.kb * 32;
+        const int pieces_per_row = kbn * 32;
         const int total = rows * pieces_per_row;
         for (int i = threadIdx.x; i < total; i += blockDim.x) {
             const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
-            const int k = cc * 8;
+            const int k = kb0 * kBlockCols + cc * 8;
             stage_piece<XVEC, false>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16, a.x + int64_t(m) * a.ldx + k,
                               m < a.m && k < a.k, k, a.k);
         }
@@ -84,7 +97,7 @@ w4a16_tile_kernel(const TileArgs a) {
     __syncthreads();        // x staged; barrier initialisation visible to every waiter
 
     // units = half blocks, dealt in consecutive runs to the warps
-    const int units = a.kb * 2;
+    const int units = kbn * 2;
     const int u0 = (units * warp) / a.warps, u1 = (units * (warp + 1)) / a.warps;
     float acc[MT][4];
 #pragma unroll
@@ -135,6 +148,54 @@ const uint32_t w[4] = {dequant_pair_even(and_or(ua, 0x000F000Fu, 0x64006400u), c
     for (int mt = 0; mt < MT; ++mt)
         red[(warp * MT + mt) * 32 + lane] = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
     __syncthreads();
+    if (a.ksplit > 1) {
+        // The CTAs of a cluster share the row tile.  Each adds its warps' tiles in warp order; CTA p > 0
+        // puts its 128 * MT sums into slot p - 1 of the first one's shared memory, and after the cluster
+        // barrier the first adds the slots to its own sums in CTA order and writes y.
+        float* tot = reinterpret_cast<float*>(red) + a.warps * MT * 128;       // [MT * 128] own sums
+        float* peer = tot + MT * 128;                                          // [ksplit - 1][MT * 128] the others' sums
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+        for (int e = threadIdx.x; e < MT * 128; e += blockDim.x) {
+            const int mt = e >> 7, rl = (e >> 2) & 31, c = e & 3;
+            float sum = 0.0f;
+            for (int w = 0; w < a.warps; ++w)
+                sum += reinterpret_cast<const float*>(red)[((w * MT + mt) * 32 + rl) * 4 + c];
+            if (part == 0) {
+                tot[e] = sum;
+            } else {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(smem_u32(peer + (part - 1) * (MT * 128) + e)));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(sum) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (part != 0) return;
+        if (a.act) {
+            for (int e = threadIdx.x; e < MT * 64; e += blockDim.x) {
+                const int mt = e >> 6, rl = (e >> 1) & 31, c = e & 1;
+                const int at = (mt * 32 + rl) * 4 + c;
+                float gate = tot[at], up = tot[at + 2];
+                for (int p = 0; p + 1 < a.ksplit; ++p) {
+                    gate += peer[p * (MT * 128) + at];
+                    up += peer[p * (MT * 128) + at + 2];
+                }
+                const int rg = rl >> 2, rt = rl & 3;
+                const int m = mt * 8 + 2 * rt + c, n = nt * 16 + rg;
+                if (m < a.m && n + 8 < a.n)
+                    a.y[int64_t(m) * a.ldy + nt * 8 + rg] = silu_mul(finish_output(gate, a.bias, n), finish_output(up, a.bias, n + 8));
+            }
+            return;
+        }
+        for (int e = threadIdx.x; e < MT * 128; e += blockDim.x) {
+            const int mt = e >> 7, rl = (e >> 2) & 31, c = e & 3;
+            float sum = tot[e];
+            for (int p = 0; p + 1 < a.ksplit; ++p) sum += peer[p * (MT * 128) + e];
+            const int rg = rl >> 2, rt = rl & 3;
+            const int m = mt * 8 + 2 * rt + (c & 1), n = nt * 16 + rg + 8 * (c >> 1);
+            if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(sum, a.bias, n);
+        }
+        return;
+    }
     // thread e adds element e of every warp's tile in warp order and stores one output
     if (a.act) {
         // gate (row rg) and up (row rg + 8) of one output: elements c and c + 2 of the same fragment

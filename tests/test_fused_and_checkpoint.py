@@ -152,7 +152,7 @@ def test_image_cache_hit_equals_repack(tmp_path):
 @pytest.mark.gpu
 @pytest.mark.parametrize("m", [1, 3, 8, 16, 33, 64, 65, 300, 1000])
 @pytest.mark.parametrize("rows,k,bias", [(1536, 1024, False), (3072, 1024, True), (1000, 4096, True), (8, 200, False),
-                                          (12288, 4096, False)])
+                                          (12288, 4096, False), (512, 3072, True)])
 def test_gate_up_silu_matches_the_separate_launches(m, rows, k, bias):
     """Fused SiLU(gate)*up against the two projections followed by torch's own FP16 silu and
     multiply on the GPU (the reference's unfused sequence), and against a CPU restatement."""

@@ -38,6 +38,10 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     assert _native.native_bytes(16, 256) == 2336 and _native.native_bytes(17, 257) == 4 * 2336
     plan = _native.plan(8, 2048, 1024)
     assert plan["route"] == "b200_tile" and plan["grid"] == 128
+    # few row tiles and a long K: a cluster of 2 or 4 CTAs per row tile, each at least 8 half blocks of K
+    assert _native.plan(1, 1024, 3072) == {"route": "b200_tile", "k_splits": 2, "grid": 128, "rows_per_launch": 1}
+    assert _native.plan(8, 512, 8192) == {"route": "b200_tile", "k_splits": 4, "grid": 128, "rows_per_launch": 8}
+    assert _native.plan(16, 1024, 1024)["k_splits"] == 1 and _native.plan(16, 4096, 4096)["k_splits"] == 1
     assert _native.plan(8, 57344, 8192)["route"] == "b200_stream"
     assert _native.plan(32, 2048, 1024)["route"] == "b200_stream"
     assert _native.plan(512, 4096, 4096)["route"] == "b200_tcgen05"

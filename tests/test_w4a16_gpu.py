@@ -398,7 +398,8 @@ def test_tcgen05_unaligned_falls_back_and_graph_replay():
 # the three decode/prefill kernel families agree with each other and with the oracle
 # ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("m,n,k", [(1, 1000, 1024), (3, 37, 257), (8, 2048, 1024), (16, 1024, 3072), (5, 12289, 1024),
-                                   (16, 4096, 4096), (1, 16, 6912), (9, 100, 264)])
+                                   (16, 4096, 4096), (1, 16, 6912), (9, 100, 264), (5, 1000, 4352), (1, 1184, 2304),
+                                   (8, 512, 8192), (16, 256, 4096), (3, 16, 7000)])
 def test_tile_and_stream_routes_agree(m, n, k):
     g = torch.Generator().manual_seed(m * 7 + n + k)
     layer = ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.03).half().cuda())
@@ -418,6 +419,9 @@ def test_tile_and_stream_routes_agree(m, n, k):
                                layer.zeros.cpu().numpy(), k)
     got = _native.linear(eye, image, n, k, route=_native.ROUTE_TILE).t().contiguous().cpu().numpy()
     assert np.array_equal(got, w[:, :eye.shape[0]])
+    tail = torch.eye(k, dtype=torch.float16, device="cuda")[max(0, k - 8):]               # the last columns of K
+    got = _native.linear(tail, image, n, k, route=_native.ROUTE_TILE).t().contiguous().cpu().numpy()
+    assert np.array_equal(got, w[:, max(0, k - 8):])
 
 
 def test_route_limits_are_reported():
@@ -425,9 +429,9 @@ def test_route_limits_are_reported():
     image = layer._native_image()
     with pytest.raises(RuntimeError, match="tile route"):
         _native.linear(torch.zeros(17, 512, dtype=torch.float16, device="cuda"), image, 64, 512, route=_native.ROUTE_TILE)
-    big = ops.QuantizedLinear.from_float(torch.randn(16, 28672, dtype=torch.float16).cuda())
+    big = ops.QuantizedLinear.from_float(torch.randn(16, 40960, dtype=torch.float16).cuda())
     with pytest.raises(RuntimeError, match="tile route"):
-        _native.linear(torch.zeros(1, 28672, dtype=torch.float16, device="cuda"), big._native_image(), 16, 28672,
+        _native.linear(torch.zeros(1, 40960, dtype=torch.float16, device="cuda"), big._native_image(), 16, 40960,
                        route=_native.ROUTE_TILE)
     with pytest.raises(RuntimeError, match="route"):
         _native.linear(torch.zeros(1, 512, dtype=torch.float16, device="cuda"), image, 64, 512, route=9)
