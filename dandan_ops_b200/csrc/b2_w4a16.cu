@@ -141,7 +141,7 @@ int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaS
 // Latency-oriented tile kernel: whole K of one row tile per CTA (small and mid-size layers).
 // ---------------------------------------------------------------------------------------
 constexpr int kTileSmemLimit = 200 * 1024;
-constexpr int64_t kTileMaxBlocks = 4096;       // native blocks (9.6 MB of image) at 5..16 rows of x; larger layers stream
+constexpr int64_t kTileMaxBlocks = 4096;       // native blocks (9.6 MB of image) at 9..16 rows of x; larger layers stream
 
 // CTAs per row tile of the tile kernel (a cluster that splits K): the largest of 4 and 2 that leaves
 // every CTA at least 8 half blocks (measured: a 1024 x 2048 layer gains 10 % from two CTAs of 8 warps, a
@@ -160,7 +160,7 @@ bool tile_applicable(int64_t rows, const b2::Dims& d, int split) {
     // Native blocks up to which one CTA per row tile beats the persistent streaming kernel (measured on
     // N x 4096 and 4096 x 8192 layers): the fewer rows of x, the less shared memory a CTA stages and the
     // more CTAs share an SM.
-    const int64_t limit = rows == 1 ? 2 * kTileMaxBlocks : rows <= 4 ? 3 * kTileMaxBlocks / 2 : kTileMaxBlocks;
+    const int64_t limit = rows == 1 ? 2 * kTileMaxBlocks : rows <= 8 ? 3 * kTileMaxBlocks / 2 : kTileMaxBlocks;
     const int smem = split > 1 ? b2::tile_smem_bytes(kb_cta, rows <= 8 ? 8 : 16, warps) + split * (rows <= 8 ? 1 : 2) * 512
                                : b2::tile_smem_bytes(d.kb, int(rows), warps);
     return int64_t(d.n16) * d.kb <= limit && smem <= kTileSmemLimit;

@@ -14,6 +14,7 @@
 //     the result is bit-reproducible and no workspace, ticket or partial tile is needed.
 // The dequantization chain and the MMA fragment layout are those of stream_kernel.cuh.
 #pragma once
+#include <type_traits>
 #include "layout.cuh"
 #include "stream_kernel.cuh"
 
@@ -39,9 +40,13 @@ struct TileArgs {
 
 // `rows` = rows of x that exist (1..16): only those are staged, so that at M = 1 a CTA of a
 // 4096-column layer needs 55 KB instead of 120 KB and four of them share an SM.
+// Staged x: per 64-column chunk `rows` rows of 128 bytes, the eight 16-byte pieces of row m stored at
+// piece index p ^ (m & 7), chunks 32 bytes apart modulo 128: the 16-byte fragment reads of a quarter
+// warp (two rows, four chunks) fall into eight different bank groups without padding the rows.
+__host__ __device__ constexpr int tile_x_chunk_bytes(int rows) { return rows * 128 + 32; }
 __host__ __device__ constexpr int tile_smem_bytes(int kb, int rows, int warps) {
     // barriers (padded to 128) + blocks + staged x + reduction tiles
-    return ((kb * 8 + 127) / 128) * 128 + kb * kBlockBytes + kb * 4 * stream_x_chunk_bytes(rows) +
+    return ((kb * 8 + 127) / 128) * 128 + kb * kBlockBytes + kb * 4 * tile_x_chunk_bytes(rows) +
            warps * (rows <= 8 ? 1 : 2) * 512;
 }
 
@@ -53,7 +58,7 @@ __global__ void __launch_bounds__(kTileMaxWarps * 32)
 w4a16_tile_kernel(const TileArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int rows = FULL ? MT * 8 : a.m;
-    const int kChunk = stream_x_chunk_bytes(rows);          // `rows` rows of 144 bytes per 64-column chunk
+    const int kChunk = tile_x_chunk_bytes(rows);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     // this CTA's share of the row tile: blocks kb0 .. kb0 + kbn - 1 of K
@@ -85,14 +90,29 @@ w4a16_tile_kernel(const TileArgs a) {
     }
     // stage x for all columns (zero beyond M and K)
     {
-        const int pieces_per_row = kbn * 32;
-        const int total = rows * pieces_per_row;
-        for (int i = threadIdx.x; i < total; i += blockDim.x) {
-            const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
-            const int k = kb0 * kBlockCols + cc * 8;
-            stage_piece<XVEC, false>(xs + (cc >> 3) * kChunk + m * 144 + (cc & 7) * 16, a.x + int64_t(m) * a.ldx + k,
-                              m < a.m && k < a.k, k, a.k);
-        }
+        // Copies that bypass registers (cp.async) are the faster form for the small grids of a K split
+        // (2 %), loads through registers for grids that fill the device (6144 x 1024: 4.5 vs 5.2 us).
+        auto stage = [&](auto async) {
+            constexpr bool kAsync = decltype(async)::value;
+            const int pieces_per_row = kbn * 32;
+            for (int cc = threadIdx.x; cc < pieces_per_row; cc += blockDim.x) {
+                const int k = kb0 * kBlockCols + cc * 8;
+                uint8_t* dst = xs + (cc >> 3) * kChunk;
+                const __half* src = a.x + k;
+                if constexpr (FULL) {
+#pragma unroll
+                    for (int m = 0; m < MT * 8; ++m)
+                        stage_piece<XVEC, kAsync>(dst + m * 128 + (((cc ^ m) & 7) << 4), src + int64_t(m) * a.ldx,
+                                                  m < a.m && k < a.k, k, a.k);
+                } else {
+                    for (int m = 0; m < rows; ++m)
+                        stage_piece<XVEC, kAsync>(dst + m * 128 + (((cc ^ m) & 7) << 4), src + int64_t(m) * a.ldx,
+                                                  k < a.k, k, a.k);
+                }
+            }
+            if constexpr (XVEC && kAsync) stage_wait();
+        };
+        if (a.ksplit > 1) stage(std::true_type{}); else stage(std::false_type{});
     }
     __syncthreads();        // x staged; barrier initialisation visible to every waiter
 
@@ -121,14 +141,14 @@ w4a16_tile_kernel(const TileArgs a) {
         const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);
         const float eg = -(64.0f + zg), eh = -(64.0f + zh);
         const uint64_t sg = twice(step.x), sh = twice(step.y);
-        const uint8_t* xchunk = xs + (b * 4 + t) * kChunk + g * 144 + h * 64;
+        const uint8_t* xchunk = xs + (b * 4 + t) * kChunk + g * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t wa = pick(ca, i), wb = pick(cb, i);
             uint4 xv[MT];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)      // rows of x that do not exist are not staged: their columns of the product are zero
-                xv[mt] = (FULL || mt * 8 + g < rows) ? *reinterpret_cast<const uint4*>(xchunk + mt * (8 * 144) + i * 16)
+                xv[mt] = (FULL || mt * 8 + g < rows) ? *reinterpret_cast<const uint4*>(xchunk + mt * (8 * 128) + (((h * 4 + i) ^ g) << 4))
                                                      : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
