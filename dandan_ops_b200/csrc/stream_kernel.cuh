@@ -299,11 +299,12 @@ __device__ __forceinline__ void stage_wait() {
 template <int MT, bool XVEC, int W, bool WAIT = true>
 __device__ __forceinline__ void stage_x(uint8_t* xs, const StreamArgs& a, int k0, int cols) {
     constexpr int MP = MT * 8;
-    constexpr int kThreads = W * 32;
-    const int pieces_per_row = cols >> 3;
-    const int total = MP * pieces_per_row;
-    for (int i = threadIdx.x; i < total; i += kThreads) {
-        const int m = i / pieces_per_row, cc = i - m * pieces_per_row;
+    // Work item = (row, column block): 32 pieces, one per lane, dealt to the warps in turn.  MP is a
+    // power of two, so the split of the item index needs no division (`cols` is a multiple of 256).
+    const int items = MP * (cols >> 8);
+    const int lane = threadIdx.x & 31;
+    for (int it = threadIdx.x >> 5; it < items; it += W) {
+        const int m = it & (MP - 1), cc = (it / MP) * 32 + lane;
         const int T = cc >> 3, c = cc & 7;
         const int k = k0 + cc * 8;
         stage_piece<XVEC>(xs + T * stream_x_chunk_bytes(MP) + m * 144 + c * 16, a.x + int64_t(m) * a.ldx + k,

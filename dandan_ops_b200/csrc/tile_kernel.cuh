@@ -8,10 +8,13 @@
 //     anything else happens (kb * 2336 bytes in flight per CTA, several CTAs per SM);
 //   * the unit of work is half a block (eight of its sixteen MMA steps); up to 16 warps take
 //     consecutive units, so a block is decoded by two warps in parallel;
-//   * x for the whole K range is staged once per CTA in the padded conflict-free layout of
-//     the streaming kernel;
+//   * x for the CTA's K range is staged once, unpadded: rows of 128 bytes per 64-column chunk
+//     with the 16-byte pieces XOR-swizzled by the row, so the fragment reads are conflict-free
+//     and two CTAs of a 4096-column layer share an SM at M = 8;
 //   * the per-warp FP32 accumulator tiles are added in warp order through shared memory, so
-//     the result is bit-reproducible and no workspace, ticket or partial tile is needed.
+//     the result is bit-reproducible and no workspace, ticket or partial tile is needed;
+//   * layers with few row tiles and a long K run a cluster of 2 or 4 CTAs per row tile, each
+//     on its share of K; the sums of CTAs 1.. reach CTA 0 through distributed shared memory.
 // The dequantization chain and the MMA fragment layout are those of stream_kernel.cuh.
 #pragma once
 #include <type_traits>
