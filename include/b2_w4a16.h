@@ -41,7 +41,8 @@ extern "C" {
                                 B2_STREAM_MAX_M rows (32 rows on layers above ~10 MB), tensor-memory GEMM above */
 #define B2_ROUTE_STREAM 1    /* persistent weight-streaming kernel (any M, re-reads the weights every 64 rows) */
 #define B2_ROUTE_TCGEN05 2   /* TMA + tcgen05 GEMM with in-kernel INT4->FP16 converter */
-#define B2_ROUTE_TILE 3      /* one CTA per 16-row tile, whole K in flight at once (M <= 16, K up to ~7k) */
+#define B2_ROUTE_TILE 3      /* one CTA (or a cluster of 2 or 4 CTAs that split K) per 16-row tile, the whole K range
+                                in flight at once (M <= 16; K as far as it fits in shared memory) */
 
 /* Largest M the weight-streaming kernel takes in one launch; B2_ROUTE_AUTO hands larger
  * batches to the tensor-memory GEMM. */
