@@ -131,9 +131,21 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             self.thread.join(timeout=2)
+
+    def hold_load(self, run, sync, min_samples, limit_s):
+        """Keep the GPU under the benchmark's own load (`run` = one step, `sync` = wait for it) until
+        `min_samples` samples have arrived or `limit_s` seconds have passed: nvidia-smi needs longer to
+        start than a short timed region lasts, so the region is embedded in a longer stretch of the
+        same back-to-back replays and every sample is taken under that load."""
+        if self.proc is None:
+            return
+        t_end = time.monotonic() + limit_s
+        while len(self.lines) < min_samples and time.monotonic() < t_end:
+            for _ in range(8):
+                run()
+            sync()
 
     def summary(self):
         sm, mx, reasons = [], [], set()
@@ -151,7 +163,9 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm),
+                "window": "back-to-back replays of the step from before the first sample until after the last; "
+                          "the timed region lies inside"}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -256,12 +270,21 @@ def run_gpu(args, rank, world, local_rank):
             replay()
         sync_all()
         with ClockSampler(local_rank) as clocks:
+            # graph replays only: a rank-dependent number of eager NCCL gathers would desynchronize the ranks
+            if use_graph:
+                clocks.hold_load(replay, stream.synchronize, 1, 8.0)
+                first = len(clocks.lines)
+            sync_all()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(args.steps):
                 replay()
             e1.record(stream)
             sync_all()
+            if use_graph:
+                clocks.hold_load(replay, stream.synchronize, first + 3, 2.0)
+            else:
+                time.sleep(0.15)
         gpu_ms = e0.elapsed_time(e1)
 
         # end to end: every call's x starts in pinned host memory and every call's y ends there.  The
