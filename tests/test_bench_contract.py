@@ -46,3 +46,32 @@ def test_gpu_arm_prints_one_contract_line():
     assert e2e["value"] > 0 and e2e["h2d_bytes_per_step"] > 0 and e2e["d2h_bytes_per_step"] > 0 and e2e["eager"]["value"] > 0
     pre = line["roofline_prefill"]
     assert pre["bound"] == "tensor" and pre["unit"] == "TFLOP/s" and 0 < pre["frac"] < 1.2
+
+
+def test_clock_sampler_holds_the_load_until_samples_arrive():
+    """The sampler keeps replaying the step until nvidia-smi has delivered its samples, and gives up
+    after its time limit when it never does (no GPU needed: the sampler process is faked)."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    sampler = bench.ClockSampler(0)
+    assert sampler.summary()["samples"] == 0
+    sampler.hold_load(lambda: pytest.fail("no sampler process: nothing to wait for"), lambda: None, 1, 1.0)
+
+    sampler.proc = object()                      # "running"
+    steps = []
+
+    def run():
+        steps.append(1)
+        if len(steps) == 24:                     # the first sample arrives during the third batch of replays
+            sampler.lines.append("1965, 1965, Not Active, Not Active, Not Active, Active\n")
+
+    sampler.hold_load(run, lambda: None, 1, 30.0)
+    assert len(steps) == 24 and sampler.summary() == {
+        "sm_mhz": 1965.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 1,
+        "window": sampler.summary()["window"]}
+
+    import time
+    t0 = time.monotonic()
+    sampler.hold_load(lambda: None, lambda: time.sleep(0.01), 5, 0.2)    # never reaches five samples
+    assert 0.2 <= time.monotonic() - t0 < 2.0
