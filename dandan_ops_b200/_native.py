@@ -167,30 +167,73 @@ def plan(m, n, k):
 # One scratch buffer per (device, stream): kernels on one stream run in order, so every
 # layer launched there can share it.  The ticket prefix is zero on allocation and every
 # kernel leaves it zero.
+#
+# A buffer that has been handed to a kernel is NEVER released: a CUDA graph captured earlier
+# holds its raw address (tickets that must stay zero, split-K partial tiles), so when a later
+# call needs more room the old buffer moves to `_retired` and stays allocated for the life of
+# the process.  Growth is geometric, which bounds the retired total by the size of the live one.
+# Graphs that were captured on one stream share that stream's buffer and must not be replayed
+# concurrently with each other; capture inside `private_workspace()` to give a graph its own.
 _workspaces = {}
+_retired = []
+_private = []        # stack of [buffer or None, minimum bytes] pushed by private_workspace()
+
+
+def _grown(device, nbytes, previous):
+    size = max(int(nbytes), 1 << 20, 2 * previous.numel() if previous is not None else 0)
+    if previous is not None:
+        _retired.append(previous)
+    return torch.zeros(size, dtype=torch.uint8, device=device)
 
 
 def workspace(device, nbytes):
+    if _private:
+        slot = _private[-1]
+        if slot[0] is None or slot[0].numel() < nbytes or slot[0].device != device:
+            slot[0] = _grown(device, max(int(nbytes), slot[1]), slot[0])
+        return slot[0]
     key = (device.index, _stream())
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        size = max(int(nbytes), 1 << 20)
-        buf = torch.zeros(size, dtype=torch.uint8, device=device)
-        _workspaces[key] = buf
+        buf = _workspaces[key] = _grown(device, nbytes, buf)
     return buf
 
 
+class private_workspace:
+    """Context manager: every call inside uses a workspace of its own instead of the current
+    stream's shared one.  Capture a CUDA graph inside it when that graph will be replayed
+    concurrently with other work of this library (another stream, another graph): calls that
+    overlap on the GPU must not share tickets and partial tiles.  The buffer lives as long as
+    the process (a captured graph keeps its address)."""
+
+    def __init__(self, min_bytes=1 << 20):
+        self.slot = [None, int(min_bytes)]
+
+    def __enter__(self):
+        _private.append(self.slot)
+        return self
+
+    def __exit__(self, *exc):
+        _private.remove(self.slot)
+        if self.slot[0] is not None:
+            _retired.append(self.slot[0])
+        return False
+
+
 def status(device=None):
-    """Sticky status word of the current stream's workspace (synchronizes; 0 = ok)."""
+    """Sticky status words of every workspace this process has used on `device`, OR-ed together
+    (synchronizes; 0 = every kernel ran to completion)."""
     lib = load()
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    result = 0
     with torch.cuda.device(device):
-        ws = _workspaces.get((device.index, _stream()))
-        if ws is None:
-            return 0
-        word = ctypes.c_uint(0)
-        _check(lib.b2_w4a16_status(ws.data_ptr(), _stream(), ctypes.byref(word)))
-    return int(word.value)
+        buffers = [b for b in list(_workspaces.values()) + _retired + [s[0] for s in _private if s[0] is not None]
+                   if b.device == device]
+        for ws in buffers:
+            word = ctypes.c_uint(0)
+            _check(lib.b2_w4a16_status(ws.data_ptr(), _stream(), ctypes.byref(word)))
+            result |= int(word.value)
+    return result
 
 
 STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
@@ -224,7 +267,7 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
     if need is None:
         need = _need_cache[key] = int(lib.b2_w4a16_workspace_bytes(m, n, k))
     stream = torch.cuda.current_stream().cuda_stream
-    ws = _workspaces.get((device.index, stream))
+    ws = None if _private else _workspaces.get((device.index, stream))
     if ws is None or ws.numel() < need:
         ws = workspace(device, need)
     rc = lib.b2_w4a16_linear_bias(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),

@@ -17,6 +17,8 @@ Reference locations restated (paths inside the reference project):
   unpack     dandan_ops/quantization.py:106-121
   dequantize dandan_ops/quantization.py:124-143
   linear     dandan_ops/quantized_linear.py:73-81  (route "reference")
+  residual_rms_norm  dandan_ops/elementwise.py:118-120, 156-161  (route "torch")
+  silu_and_mul       dandan_ops/elementwise.py:168-172           (route "torch")
 
 All arithmetic that the reference performs in FP32 is performed here on
 np.float32 arrays so that every intermediate is rounded exactly as torch rounds it.
@@ -152,6 +154,29 @@ def within_tolerance(actual, expected, atol: float = 2e-3, rtol: float = 2e-3) -
     a = np.asarray(actual).astype(np.float64)
     e = np.asarray(expected).astype(np.float64)
     return bool((np.abs(a - e) <= atol + rtol * np.abs(e)).all())
+
+
+def residual_rms_norm(x, residual, weight, eps: float):
+    """(RMSNorm(x + residual) * weight, x + residual) for FP16 inputs, as the reference's CPU
+    route computes them (dandan_ops/elementwise.py:156-161 with `_rms_reference`, :118-120): the
+    sum is rounded to FP16 first, the mean of squares and the scaling run in FP32, the
+    normalized value is rounded to FP16 before the FP16 multiplication by the weight."""
+    xa = np.asarray(x, dtype=np.float16)
+    summed = xa if residual is None else (xa + np.asarray(residual, dtype=np.float16)).astype(np.float16)
+    work = summed.astype(_F32)
+    mean_sq = (work * work).mean(axis=-1, keepdims=True, dtype=_F32)
+    inverse = (_F32(1) / np.sqrt(mean_sq + _F32(eps))).astype(_F32)
+    normed = (work * inverse).astype(np.float16)
+    return (normed * np.asarray(weight, dtype=np.float16)).astype(np.float16), summed
+
+
+def silu_and_mul(gate, up):
+    """SiLU(gate) * up on FP16 inputs (dandan_ops/elementwise.py:168-172): the activation is
+    evaluated in FP32, rounded to FP16, then multiplied by `up` in FP16."""
+    g = np.asarray(gate, dtype=np.float16).astype(_F32)
+    with np.errstate(over="ignore"):
+        act = (g / (_F32(1) + np.exp(-g))).astype(np.float16)
+    return (act * np.asarray(up, dtype=np.float16)).astype(np.float16)
 
 
 def storage_bytes(n: int, k: int, group_size: int = GROUP) -> int:
