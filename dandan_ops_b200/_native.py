@@ -15,7 +15,7 @@ ROUTE_AUTO, ROUTE_STREAM, ROUTE_TCGEN05, ROUTE_TILE = 0, 1, 2, 3
 ROUTE_NAMES = {ROUTE_STREAM: "b200_stream", ROUTE_TCGEN05: "b200_tcgen05", ROUTE_TILE: "b200_tile"}
 GEMM_SHAPES = {"auto": 0, "128x128": 1, "256x128": 2, "256x192": 3, "pair256": 4, "pair192": 5}
 STREAM_MAX_M = 64
-TICKET_BYTES = 16384
+TICKET_BYTES = 32768
 
 _lib = None
 _lock = threading.Lock()
@@ -26,6 +26,7 @@ _SIGNATURES = {
     "b2_w4a16_last_error": (ctypes.c_char_p, []),
     "b2_w4a16_launch_count": (_i64, []),
     "b2_w4a16_set_gemm_shape": (_int, [_int, _int]),
+    "b2_w4a16_test_hooks": (_int, [_int, _int, _int]),
     "b2_w4a16_native_bytes": (_i64, [_i64, _i64]),
     "b2_w4a16_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "b2_w4a16_unrepack": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
@@ -97,6 +98,13 @@ def set_gemm_shape(name="auto", k_splits=0):
     CTAs along K) for every later call (tests, tuning); "auto" / 0 restore the cost model."""
     _check(load().b2_w4a16_set_gemm_shape(GEMM_SHAPES[name], k_splits))
     _need_cache.clear()          # the workspace a problem needs depends on the shape
+
+
+def test_hooks(wait_limit=0, skip_copy=-1, stream_variant=0):
+    """Test hooks of the decode kernels (see include/b2_w4a16.h): poll limit of the bounded waits,
+    one weight copy to leave out in the next launch, streaming-kernel form."""
+    _check(load().b2_w4a16_test_hooks(wait_limit, skip_copy, stream_variant))
+    _need_cache.clear()
 
 
 def native_bytes(n, k):

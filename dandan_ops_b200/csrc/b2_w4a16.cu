@@ -13,6 +13,7 @@
 #include "layout.cuh"
 #include "layout_kernels.cuh"
 #include "stream_kernel.cuh"
+#include "stream2_kernel.cuh"
 #include "gemm_kernel.cuh"
 #include "gemm_pair_kernel.cuh"
 #include "tile_kernel.cuh"
@@ -74,10 +75,17 @@ int check_dims(int64_t n, int64_t k) {
 // ---------------------------------------------------------------------------------------
 // Launch plan of the streaming kernel (stream-K over persistent CTAs).
 // ---------------------------------------------------------------------------------------
+// Test hooks (b2_w4a16_test_hooks): the poll limit of the kernels' bounded waits and a one-shot request to
+// leave one weight copy out, so that a test can watch a wait run out without anything hanging.
+std::atomic<int> g_wait_limit{b2::kWaitLimit};
+std::atomic<int> g_fault_step{-1};
+std::atomic<int> g_stream_variant{0};     // 0/1 = w4a16_stream_kernel; 2 = w4a16_stream2_kernel with 32 warps wherever it applies;
+                                          // 3 = w4a16_stream2_kernel with 16 warps (M <= 16)
+
 struct StreamPlan {
     int mt;            // 8-row tiles of x per launch: 1, 2, 4 or 8
     int rows;          // rows of x per launch = min(m, 64)
-    int warps;         // warps (row tiles) per CTA: 16 or 4
+    int warps;         // warps (row tiles) per CTA: 32 (w4a16_stream2_kernel), 16 or 4
     int groups;        // row groups = ceil(n16 / warps)
     long long steps;   // groups * column blocks
     int grid;          // persistent CTAs
@@ -95,9 +103,18 @@ StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     const long long steps16 = (long long)((d.n16 + 15) / 16) * d.kb;
     p.warps = (steps16 >= 2LL * sms && p.mt <= 4) ? 16 : 4;
     if (p.mt == 8) p.warps = 16;                      // the 16 KB x buffer of a 4-warp CTA cannot hold 64 rows
+    // The 32-warp form (w4a16_stream2_kernel) runs only when asked for (b2_w4a16_test_hooks): measured on the
+    // 8B/70B projections it is 5-15 % behind the 16-warp kernels (more warps per scheduler, but more
+    // instructions per block under the 64-register cap).
+    const long long steps32 = (long long)((d.n16 + 31) / 32) * d.kb;
+    const int variant = g_stream_variant.load(std::memory_order_relaxed);
+    if (p.mt <= 2 && variant == 2 && steps32 >= sms) p.warps = 32;
     p.groups = (d.n16 + p.warps - 1) / p.warps;
     p.steps = (long long)p.groups * d.kb;
-    const long long slots = (long long)sms * (p.warps == 16 ? B2_STREAM_CTAS16 : 4);
+    long long slots = (long long)sms * (p.warps == 32 ? 1 : p.warps == 16 ? B2_STREAM_CTAS16 : 4);
+    // one ticket per row tile of a split row group: at most min(groups, grid) * warps of them
+    const long long ticket_slots = B2_W4A16_TICKET_BYTES / 4 - 1;
+    if (p.groups > slots && slots * p.warps > ticket_slots) slots = ticket_slots / p.warps;
     p.grid = int(p.steps < slots ? p.steps : slots);
     const long long per_cta = p.steps / p.grid;       // >= 1
     long long parts = (d.kb + per_cta - 1) / per_cta + 1;
@@ -126,8 +143,30 @@ int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
     return after_launch("w4a16_stream_kernel");
 }
 
+template <int MT, bool XVEC, int W>
+int launch_stream2_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_stream2_kernel<MT, XVEC, W>;
+    constexpr int smem = b2::s2_smem_bytes(MT);
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<grid, W * 32, smem, s>>>(a);
+    return after_launch("w4a16_stream2_kernel");
+}
+
 template <int MT>
 int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaStream_t s) {
+    if constexpr (MT <= 2) {
+        if (warps == 32) return xvec ? launch_stream2_one<MT, true, 32>(a, grid, s) : launch_stream2_one<MT, false, 32>(a, grid, s);
+        if (warps == 16 && g_stream_variant.load(std::memory_order_relaxed) == 3)
+            return xvec ? launch_stream2_one<MT, true, 16>(a, grid, s) : launch_stream2_one<MT, false, 16>(a, grid, s);
+    }
     if constexpr (MT == 8) {
         return xvec ? launch_stream_one<MT, true, 16>(a, grid, s) : launch_stream_one<MT, false, 16>(a, grid, s);
     } else {
@@ -211,6 +250,8 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.bias = static_cast<const __half*>(bias);
     a.ldx = ldx; a.ldy = ldy;
     a.m = int(rows); a.n = d.n; a.k = d.k; a.n16 = d.n16; a.kb = d.kb;
+    a.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
+    a.fault_block = g_fault_step.exchange(-1, std::memory_order_relaxed);
     const int mt = rows <= 8 ? 1 : 2;
     // Two CTAs per row tile (a cluster, K halved) when the tiles leave more than half of the SMs idle and
     // a CTA's 16 warps would each take more than one unit: the pair finishes in one round instead of two.
@@ -259,6 +300,8 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.m = int(rows); a.n = d.n; a.k = d.k;
         a.n16 = d.n16; a.kb = d.kb;
         a.groups = p.groups; a.max_parts = p.max_parts; a.steps = int(p.steps);
+        a.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
+        a.fault_step = g_fault_step.exchange(-1, std::memory_order_relaxed);
         int rc;
         switch (p.mt) {
             case 1: rc = launch_stream<1>(a, xvec, p.warps, p.grid, s); break;
@@ -540,6 +583,14 @@ const char* b2_w4a16_last_error(void) { return g_error.c_str(); }
 
 int64_t b2_w4a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int b2_w4a16_test_hooks(int wait_limit, int skip_copy, int stream_variant) {
+    if (stream_variant < 0 || stream_variant > 3) return fail(B2_ERR_ARGUMENT, "stream_variant must be 0..3");
+    g_wait_limit.store(wait_limit > 0 ? wait_limit : b2::kWaitLimit, std::memory_order_relaxed);
+    g_fault_step.store(skip_copy >= 0 ? skip_copy : -1, std::memory_order_relaxed);
+    g_stream_variant.store(stream_variant, std::memory_order_relaxed);
+    return B2_OK;
+}
+
 int b2_w4a16_set_gemm_shape(int shape, int k_splits) {
     if (shape < B2_GEMM_SHAPE_AUTO || shape > B2_GEMM_SHAPE_PAIR_192)
         return fail(B2_ERR_ARGUMENT, "unknown GEMM tile shape");
@@ -639,7 +690,12 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
 }
 
 int b2_w4a16_status(const void* workspace, void* stream, unsigned* status_host) {
-    if (!workspace || !status_host) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (!status_host) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (!workspace) {                                  // the scratch built into the library (b2_w4a16_linear_static)
+        void* scratch = nullptr;
+        if (int rc = static_scratch(&scratch)) return rc;
+        workspace = scratch;
+    }
     const unsigned* word = static_cast<const unsigned*>(workspace) + (B2_W4A16_TICKET_BYTES / 4 - 1);
     cudaError_t e = cudaMemcpyAsync(status_host, word, sizeof(unsigned), cudaMemcpyDeviceToHost,
                                     static_cast<cudaStream_t>(stream));
@@ -904,8 +960,9 @@ int b2_w4a16_linear_static(const void* x, int64_t ldx, const void* native, void*
                     std::to_string(B2_W4A16_STATIC_SCRATCH_BYTES) + " (use b2_w4a16_linear with a workspace)");
     void* scratch = nullptr;
     if (int rc = static_scratch(&scratch)) return rc;
-    // The array keeps whatever the previous call left; the tickets must start at zero.
-    const cudaError_t e = cudaMemsetAsync(scratch, 0, B2_W4A16_TICKET_BYTES, static_cast<cudaStream_t>(stream));
+    // The array keeps whatever the previous call left; the tickets must start at zero.  The last word
+    // of the ticket area is the sticky status word, which survives (b2_w4a16_status(NULL, ...) reads it).
+    const cudaError_t e = cudaMemsetAsync(scratch, 0, B2_W4A16_TICKET_BYTES - 4, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail("cudaMemsetAsync", e);
     return b2_w4a16_linear_route(x, ldx, native, y, ldy, m, n, k, scratch, B2_W4A16_STATIC_SCRATCH_BYTES, stream,
                                  B2_ROUTE_STREAM);

@@ -80,6 +80,9 @@ struct StreamArgs {
                             //    y[:, 8*tile + g] = silu_mul(gate, up), y has n/2 columns
     int max_parts;          // partial slots per row tile
     int steps;              // groups * kb (below 2^20 for every layer the index checks admit)
+    int wait_limit;         // mbarrier polls before a warp gives up (kWaitLimit; a test passes a small number)
+    int fault_step;         // -1; a test passes n >= 0: warp 0 of CTA 0 arms the barrier of its n-th weight
+                            // copy but does not issue the copy, so that the wait for it runs out
 };
 
 // ---- small PTX helpers ------------------------------------------------------------------
@@ -258,8 +261,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait: false if the phase did not complete within kWaitLimit polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < kWaitLimit; ++i)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = kWaitLimit) {
+    for (int i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
@@ -362,9 +365,10 @@ w4a16_stream_kernel(const StreamArgs a) {
     int fgrp = int(b0 / a.kb);
     int fkb = b0 - fgrp * a.kb;
     const uint8_t* fptr = a.native + ((long long)fkb * a.n16 + fgrp * kWarps + warp) * kBlockBytes;
+    int fault = (a.fault_step >= 0 && blockIdx.x == 0 && warp == 0) ? a.fault_step : -1;   // test hook, see StreamArgs
     auto request = [&](int slot) {
         mbar_expect_tx(bar0 + slot * 8, kBlockBytes);
-        bulk_copy_g2s(ring0 + slot * kBlockBytes, fptr, kBlockBytes, bar0 + slot * 8);
+        if (fault-- != 0) bulk_copy_g2s(ring0 + slot * kBlockBytes, fptr, kBlockBytes, bar0 + slot * 8);
         ++fetch;
         fptr += stride;
         if (++fkb == a.kb) {
@@ -415,7 +419,7 @@ w4a16_stream_kernel(const StreamArgs a) {
             const int xorigin = whole_x ? 0 : p0;          // column block that the x buffer starts at
             if (!active || failed) continue;
             for (int kb = p0; kb < p1; ++kb) {
-                if (!mbar_wait(bar0 + stage * 8, parity)) {
+                if (!mbar_wait(bar0 + stage * 8, parity, a.wait_limit)) {
                     failed = true;
                     if (lane == 0) atomicOr(a.status, kStatusCopyTimeout);
                     break;
@@ -526,11 +530,11 @@ w4a16_stream_kernel(const StreamArgs a) {
     }
 
     if (failed) {
-        // Let copies that are still in flight land before the CTA's shared memory is released.
+        // Let copies that are still in flight land before the CTA's shared memory is released
+        // (a bounded look at every slot of this warp's ring).
         for (int s = 0; s < kStages; ++s) {
             bool landed = false;
             for (int i = 0; i < 4096 && !landed; ++i) landed = mbar_try_wait(bar0 + stage * 8, parity);
-            if (!landed) break;
             if (++stage == kStages) { stage = 0; parity ^= 1u; }
         }
     }

@@ -36,6 +36,8 @@ struct TileArgs {
     int n16, kb;
     int warps;              // warps per CTA = min(16, 2*kb)
     int act;                // as StreamArgs::act
+    int wait_limit;         // mbarrier polls before a warp gives up (a test passes a small number)
+    int fault_block;        // -1; a test passes b >= 0: CTA 0 arms the barrier of its b-th block but skips the copy
     int ksplit;             // 1, 2 or 4: a cluster of that many CTAs shares a row tile, each takes its share
                             // of the K blocks and the others hand their 16 x 8*MT sums to the first through
                             // distributed shared memory (layers whose row tiles leave most SMs idle)
@@ -88,7 +90,8 @@ w4a16_tile_kernel(const TileArgs a) {
         const int64_t stride = int64_t(a.n16) * kBlockBytes;
         for (int b = 0; b < kbn; ++b) {
             mbar_expect_tx(bar0 + b * 8, kBlockBytes);
-            bulk_copy_g2s(smem_u32(blocks + b * kBlockBytes), src + b * stride, kBlockBytes, bar0 + b * 8);
+            if (!(blockIdx.x == 0 && b == a.fault_block))
+                bulk_copy_g2s(smem_u32(blocks + b * kBlockBytes), src + b * stride, kBlockBytes, bar0 + b * 8);
         }
     }
     // stage x for all columns (zero beyond M and K)
@@ -130,7 +133,7 @@ w4a16_tile_kernel(const TileArgs a) {
     bool failed = false;
     for (int u = u0; u < u1 && !failed; ++u) {
         const int b = u >> 1, h = u & 1;
-        if (!mbar_wait(bar0 + b * 8, 0)) {
+        if (!mbar_wait(bar0 + b * 8, 0, a.wait_limit)) {
             failed = true;
             if (lane == 0 && a.status) atomicOr(a.status, kStatusCopyTimeout);
             break;
@@ -167,6 +170,14 @@ const uint32_t w[4] = {dequant_pair_even(and_or(ua, 0x000F000Fu, 0x64006400u), c
         }
     }
     // Blocks this CTA requested but no warp waited for cannot exist: every block has two units.
+    if (__syncthreads_or(failed) && threadIdx.x == 0) {
+        // A warp gave up: copies of this CTA may still be in flight.  Look at every block's barrier
+        // once more (bounded) so that nothing lands in shared memory after the CTA has left.
+        for (int b = 0; b < kbn; ++b) {
+            bool landed = false;
+            for (int i = 0; i < 4096 && !landed; ++i) landed = mbar_try_wait(bar0 + b * 8, 0);
+        }
+    }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
         red[(warp * MT + mt) * 32 + lane] = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);

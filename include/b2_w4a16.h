@@ -50,7 +50,7 @@ extern "C" {
 
 /* Every workspace starts with this many bytes of arrival counters (one per 16-row tile;
  * K is only split when a layer has fewer row tiles than this). */
-#define B2_W4A16_TICKET_BYTES 16384
+#define B2_W4A16_TICKET_BYTES 32768
 
 /* Contract version of the packed format and numerics; 2, as the reference's
  * `w4a16_contract_version` op (dandan_ops/csrc/operators.cu:260). */
@@ -102,7 +102,8 @@ int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
 /* Reads the workspace's sticky status word into *status_host (0 = every kernel that used
  * the workspace ran to completion; bit 0 = a warp gave up waiting for a weight copy and
- * the outputs of that call are undefined).  SYNCHRONIZES the stream; diagnostics only. */
+ * the outputs of that call are undefined).  workspace == NULL reads the word of the scratch built
+ * into the library (b2_w4a16_linear_static).  SYNCHRONIZES the stream; diagnostics only. */
 int b2_w4a16_status(const void* workspace, void* stream, unsigned* status_host);
 
 /* y = x @ W^T for one layer.  Replaces the four reference ops
@@ -129,13 +130,15 @@ int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int
  *
  * The scratch is one fixed array of B2_W4A16_STATIC_SCRATCH_BYTES in device memory; every
  * GPU that loads this library holds it until the process exits.  Limits and rules:
- *   - m <= B2_STREAM_MAX_M and b2_w4a16_workspace_bytes(m,n,k) <= B2_W4A16_STATIC_SCRATCH_BYTES,
- *     otherwise B2_ERR_RANGE with a message naming both sizes (always uses the streaming
- *     kernel);
+ *   - m <= B2_STREAM_MAX_M, and the tickets plus split-K partial tiles of the streaming kernel's
+ *     plan for (m,n,k) must fit in B2_W4A16_STATIC_SCRATCH_BYTES (never more than
+ *     b2_w4a16_workspace_bytes(m,n,k)); otherwise B2_ERR_RANGE with a message naming both sizes
+ *     (the call always uses the streaming kernel);
  *   - the first call on a device looks up the array's device address (one runtime query, no
  *     allocation); make that first call before starting any stream capture;
  *   - all calls on a device share the array and it keeps the previous call's contents; each
- *     call re-zeroes the part that must start at zero (an async memset on `stream`);
+ *     call re-zeroes the part that must start at zero (an async memset on `stream`); the sticky
+ *     status word is kept and b2_w4a16_status(NULL, stream, &word) reads it;
  *   - two calls that overlap on the GPU (different streams, or graphs replayed concurrently)
  *     race on the array: serialize them, or give one of them b2_w4a16_linear and a workspace. */
 #define B2_W4A16_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
@@ -220,6 +223,15 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
  * workspace cannot take (fewer than four 256-column blocks per CTA, too many tiles for the ticket
  * area, workspace smaller than b2_w4a16_workspace_bytes()) is reduced. */
 int b2_w4a16_set_gemm_shape(int shape, int k_splits);
+
+/* Test hooks, no counterpart in the reference.  wait_limit: polls after which a kernel's bounded
+ * wait for a weight copy gives up (<= 0 restores the default, about a million).  skip_copy >= 0: the
+ * NEXT decode-kernel launch (tile or streaming) arms the barrier of that copy of its first CTA but does
+ * not issue the copy, so the wait runs out, the warp records bit 0 in the status word, drains its other
+ * copies and the kernel returns - nothing hangs; -1 = off.  stream_variant: 0 or 1 = the shipped
+ * streaming kernel; 2 / 3 = the double-buffered form with 32 / 16 warps per CTA (M <= 16), kept for
+ * measurements. */
+int b2_w4a16_test_hooks(int wait_limit, int skip_copy, int stream_variant);
 
 /* Number of kernels this library has launched from the calling process so far. */
 int64_t b2_w4a16_launch_count(void);
