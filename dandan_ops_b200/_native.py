@@ -27,6 +27,10 @@ _SIGNATURES = {
     "b2_w4a16_launch_count": (_i64, []),
     "b2_w4a16_set_gemm_shape": (_int, [_int, _int]),
     "b2_w4a16_test_hooks": (_int, [_int, _int, _int]),
+    "b2_w4a16_gather": (_int, [ctypes.POINTER(_vp), ctypes.POINTER(_vp), _int, _int, _i64, _i64, _i64, _i64, _vp]),
+    "b2_w4a16_gather_status": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_uint)]),
+    "b2_w4a16_gather_wait_limit": (_int, [_i64]),
+    "b2_w4a16_noop": (_int, [_vp]),
     "b2_w4a16_native_bytes": (_i64, [_i64, _i64]),
     "b2_w4a16_repack": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "b2_w4a16_unrepack": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
@@ -105,6 +109,34 @@ def test_hooks(wait_limit=0, skip_copy=-1, stream_variant=0):
     one weight copy to leave out in the next launch, streaming-kernel form."""
     _check(load().b2_w4a16_test_hooks(wait_limit, skip_copy, stream_variant))
     _need_cache.clear()
+
+
+GATHER_FLAG_BYTES = 128
+
+
+def gather(y_ptrs, flag_ptrs, rank, m, ld, col0, cols):
+    """`b2_w4a16_gather` on the current stream: `y_ptrs` / `flag_ptrs` are per-rank device addresses
+    (ints) of the [m, ld] FP16 buffers and flag blocks as mapped into this process."""
+    world = len(y_ptrs)
+    ys = (_vp * world)(*y_ptrs)
+    fs = (_vp * world)(*flag_ptrs)
+    _check(load().b2_w4a16_gather(ys, fs, rank, world, m, ld, col0, cols, _stream()))
+
+
+def gather_status(flag_ptr):
+    word = ctypes.c_uint(0)
+    _check(load().b2_w4a16_gather_status(flag_ptr, _stream(), ctypes.byref(word)))
+    return int(word.value)
+
+
+def gather_wait_limit(microseconds=0):
+    """How long a gather kernel waits for its peers before it gives up (0 = the default, 5 s)."""
+    _check(load().b2_w4a16_gather_wait_limit(microseconds))
+
+
+def noop():
+    """An empty kernel on the current stream (launch floor of a graph node)."""
+    _check(load().b2_w4a16_noop(_stream()))
 
 
 def native_bytes(n, k):

@@ -17,6 +17,7 @@
 #include "gemm_kernel.cuh"
 #include "gemm_pair_kernel.cuh"
 #include "tile_kernel.cuh"
+#include "gather_kernel.cuh"
 
 namespace {
 
@@ -79,6 +80,7 @@ int check_dims(int64_t n, int64_t k) {
 // leave one weight copy out, so that a test can watch a wait run out without anything hanging.
 std::atomic<int> g_wait_limit{b2::kWaitLimit};
 std::atomic<int> g_fault_step{-1};
+std::atomic<long long> g_gather_wait_ns{5000000000LL};   // five seconds
 std::atomic<int> g_stream_variant{0};     // 0/1 = w4a16_stream_kernel; 2 = w4a16_stream2_kernel with 32 warps wherever it applies;
                                           // 3 = w4a16_stream2_kernel with 16 warps (M <= 16)
 
@@ -591,6 +593,11 @@ int b2_w4a16_test_hooks(int wait_limit, int skip_copy, int stream_variant) {
     return B2_OK;
 }
 
+int b2_w4a16_gather_wait_limit(int64_t microseconds) {
+    g_gather_wait_ns.store(microseconds > 0 ? microseconds * 1000LL : 5000000000LL, std::memory_order_relaxed);
+    return B2_OK;
+}
+
 int b2_w4a16_set_gemm_shape(int shape, int k_splits) {
     if (shape < B2_GEMM_SHAPE_AUTO || shape > B2_GEMM_SHAPE_PAIR_192)
         return fail(B2_ERR_ARGUMENT, "unknown GEMM tile shape");
@@ -718,6 +725,9 @@ int64_t b2_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 }  // extern "C"
 
 namespace {
+
+// Empty kernel: the launch floor of a graph node, for benchmarks.
+__global__ void noop_kernel() {}
 
 // Elementwise fallback of the fused gate/up epilogue for batches the decode kernels do not take:
 // in[m][16 j + g] is the gate and in[m][16 j + 8 + g] the up value of output column 8 j + g.
@@ -966,6 +976,51 @@ int b2_w4a16_linear_static(const void* x, int64_t ldx, const void* native, void*
     if (e != cudaSuccess) return cuda_fail("cudaMemsetAsync", e);
     return b2_w4a16_linear_route(x, ldx, native, y, ldy, m, n, k, scratch, B2_W4A16_STATIC_SCRATCH_BYTES, stream,
                                  B2_ROUTE_STREAM);
+}
+
+int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int rank, int world, int64_t m, int64_t ld,
+                    int64_t col0, int64_t cols, void* stream) {
+    if (!y_ranks || !flag_blocks) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (world < 1 || world > b2::kGatherMaxRanks || rank < 0 || rank >= world)
+        return fail(B2_ERR_ARGUMENT, "rank / world out of range (at most 16 ranks)");
+    if (m < 0 || cols < 0 || col0 < 0 || ld < col0 + cols) return fail(B2_ERR_ARGUMENT, "slice outside the row");
+    if (m > INT_MAX) return fail(B2_ERR_RANGE, "m exceeds the kernel index range");
+    b2::GatherArgs a;
+    bool vec = col0 % 8 == 0 && cols % 8 == 0 && ld % 8 == 0;
+    for (int q = 0; q < b2::kGatherMaxRanks; ++q) {
+        a.y[q] = q < world ? static_cast<__half*>(y_ranks[q]) : nullptr;
+        a.flags[q] = q < world ? static_cast<unsigned*>(flag_blocks[q]) : nullptr;
+        if (q < world) {
+            if (!a.flags[q] || (!a.y[q] && m * cols > 0)) return fail(B2_ERR_ARGUMENT, "null pointer");
+            if (reinterpret_cast<uintptr_t>(a.flags[q]) % 4 || reinterpret_cast<uintptr_t>(a.y[q]) % 2)
+                return fail(B2_ERR_ARGUMENT, "misaligned buffer");
+            vec = vec && reinterpret_cast<uintptr_t>(a.y[q]) % 16 == 0;
+        }
+    }
+    a.rank = rank; a.world = world; a.m = int(m); a.ld = ld; a.col0 = col0; a.cols = cols;
+    a.wait_ns = g_gather_wait_ns.load(std::memory_order_relaxed);
+    DeviceInfo dev;
+    if (int rc = device_info(dev)) return rc;
+    const int64_t items = m * (vec ? cols / 8 : cols) * (world - 1);
+    const int64_t want = (items + 255) / 256;
+    const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(want, 2LL * (dev.sm_count > 0 ? dev.sm_count : 148))));
+    if (vec) b2::gather_push_wait_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    else b2::gather_push_wait_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    return after_launch("gather_push_wait_kernel");
+}
+
+int b2_w4a16_gather_status(const void* flag_block, void* stream, unsigned* status_host) {
+    if (!flag_block || !status_host) return fail(B2_ERR_ARGUMENT, "null pointer");
+    cudaError_t e = cudaMemcpyAsync(status_host, static_cast<const unsigned*>(flag_block) + b2::kGatherStatusWord,
+                                    sizeof(unsigned), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail("b2_w4a16_gather_status", e);
+    return B2_OK;
+}
+
+int b2_w4a16_noop(void* stream) {
+    noop_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
+    return after_launch("noop_kernel");
 }
 
 int b2_w4a16_linear(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,

@@ -1,0 +1,115 @@
+// All-gather of column slices over NVLink with plain peer stores (multi-GPU form of the operator).
+//
+// Every rank owns the columns [col0, col0 + cols) of an [M, N] FP16 output and has already written
+// them into its OWN copy of the full buffer (the projection kernels store straight into that
+// slice).  This kernel pushes the slice into the same place of every peer's buffer with ordinary
+// st.global through peer-mapped pointers - 16-byte stores, coalesced along a row - and then runs a
+// flag exchange: the last CTA to finish publishes this call's epoch number in every peer's flag
+// block (st.release.sys after a system-wide fence) and waits until every peer's epoch has arrived
+// in its own block.  When the kernel ends, the local buffer holds all slices.
+//
+// Nothing here reads another GPU's memory, no TMA or bulk copy touches a peer, nothing is
+// multicast.  The wait is bounded: after `wait_ns` nanoseconds the kernel records bit 2 in the flag
+// block's status word and returns, so a rank whose peer never arrives (it crashed, or was never
+// launched) gets an error status instead of a hung GPU.
+//
+// Flag block (one per rank, in memory every peer can write): 32 unsigned words
+//   [0..15] arrive[q]  epoch of the last call whose slice from rank q has landed here (written by q)
+//   [16]    epoch      number of calls this rank has completed (local)
+//   [17]    ticket     CTA arrival counter of the running call (local, zero between calls)
+//   [18]    status     sticky error bits (local): bit 2 = a peer's epoch did not arrive in time
+// Epochs only grow, so one flag block serves every gathered layer of a process as long as all ranks
+// issue the same sequence of gathers.
+#pragma once
+#include <cstdint>
+#include <cuda_fp16.h>
+
+namespace b2 {
+
+constexpr int kGatherMaxRanks = 16;
+constexpr int kGatherEpochWord = 16, kGatherTicketWord = 17, kGatherStatusWord = 18;
+constexpr unsigned kStatusPeerTimeout = 4u;
+
+struct GatherArgs {
+    __half* y[kGatherMaxRanks];         // every rank's [M, ld] buffer as mapped into this process; y[rank] is local
+    unsigned* flags[kGatherMaxRanks];   // every rank's flag block
+    int rank, world;
+    int m;
+    int64_t ld, col0, cols;
+    long long wait_ns;                  // how long the wait for the peers' flags may last before it gives up
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+gather_push_wait_kernel(const GatherArgs a) {
+    __shared__ int is_last;
+    const __half* src = a.y[a.rank];
+    const int peers = a.world - 1;
+    if (VEC) {
+        const int64_t pieces = a.cols >> 3;                      // 16-byte pieces per row
+        const int64_t per_peer = int64_t(a.m) * pieces;
+        const int64_t total = per_peer * peers;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+            const int pi = int(i / per_peer);
+            const int64_t r = i - pi * per_peer;
+            const int64_t row = r / pieces, piece = r - row * pieces;
+            const int64_t at = row * a.ld + a.col0 + piece * 8;
+            const uint4 v = *reinterpret_cast<const uint4*>(src + at);
+            *reinterpret_cast<uint4*>(a.y[pi < a.rank ? pi : pi + 1] + at) = v;
+        }
+    } else {
+        const int64_t per_peer = int64_t(a.m) * a.cols;
+        const int64_t total = per_peer * peers;
+        for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+            const int pi = int(i / per_peer);
+            const int64_t r = i - pi * per_peer;
+            const int64_t row = r / a.cols, col = r - row * a.cols;
+            const int64_t at = row * a.ld + a.col0 + col;
+            a.y[pi < a.rank ? pi : pi + 1][at] = src[at];
+        }
+    }
+    unsigned* mine = a.flags[a.rank];
+    __threadfence_system();                                      // this thread's peer stores before the ticket
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(mine + kGatherTicketWord, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence_system();
+    const unsigned epoch = mine[kGatherEpochWord] + 1u;
+    if (threadIdx.x < a.world && int(threadIdx.x) != a.rank) {
+        const int q = threadIdx.x;
+        st_release_sys(a.flags[q] + a.rank, epoch);              // my slice has landed in q's buffer
+        // Bounded by the clock and by a poll count (a poll takes at least the 64 ns sleep, so the count
+        // alone ends the loop even if the timer stood still).
+        const unsigned long long t0 = global_ns();
+        bool arrived = false;
+        for (long long i = 0; i < a.wait_ns && !arrived; ++i) {
+            arrived = int(ld_acquire_sys(mine + q) - epoch) >= 0;
+            if (arrived || global_ns() - t0 > (unsigned long long)a.wait_ns) break;
+            __nanosleep(64);
+        }
+        if (!arrived) atomicOr(mine + kGatherStatusWord, kStatusPeerTimeout);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mine[kGatherEpochWord] = epoch;
+        mine[kGatherTicketWord] = 0u;
+    }
+}
+
+}  // namespace b2

@@ -6,12 +6,23 @@ own slice of the weight image from its own HBM and produces `y[:, n0:n1]`.  A fo
 row-parallel layer consumes that slice directly.  Only when the caller asks for the full
 output are the slices gathered - one NCCL all-gather over NVLink on the compute stream.
 
+Two forms of that gather exist.  `PeerArena` + `ColumnShardedLinear.attach_arena()`: the full
+`[M, N]` output lives in memory that every rank maps (torch's symmetric memory: one allocation per
+rank, peer-mapped over NVLink), the projection kernel stores its slice straight into the local
+copy, and ONE more launch (`b2_w4a16_gather`) pushes the slice into every peer's copy with plain
+stores and exchanges epoch flags with a bounded wait - no NCCL call, no padding or permute pass,
+capturable into a CUDA graph.  Without an arena the slices go through NCCL's
+`all_gather_into_tensor` (also what the CPU/gloo tests of the host logic run).
+
 The reference is single-GPU; this module is the multi-GPU form of its QuantizedLinear.
 One process per GPU, `torch.distributed` already initialised by the caller.
 """
+import warnings
+
 import torch
 import torch.distributed as dist
 
+from . import _native
 from .quantized_linear import QuantizedLinear
 
 ROW_ALIGN = 16   # native tile height: shards start on tile boundaries
@@ -29,6 +40,65 @@ def shard_rows(out_features, world_size, rank, align=ROW_ALIGN):
     return start, stop
 
 
+class PeerArena:
+    """Memory that every rank of `group` can write: one symmetric allocation per rank holding the
+    flag block of the gather kernel and, behind it, the gathered output buffers.  Construction is
+    a collective call (every rank, same `nbytes`).  Buffers are carved out in call order, so all
+    ranks must request them in the same order (they do: the model code is the same everywhere)."""
+
+    ALIGN = 256
+
+    def __init__(self, nbytes, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+
+        group = dist.group.WORLD if group is None else group
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            try:
+                symm.set_backend("CUDA")
+            except Exception:          # already fixed by an earlier allocation
+                pass
+            symm.enable_symm_mem_for_group(group.group_name)
+        self.group = group
+        self.bytes = int(nbytes) + self.ALIGN
+        self.storage = symm.empty(self.bytes, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.storage, group)
+        self.rank, self.world = int(self.handle.rank), int(self.handle.world_size)
+        if self.world > 16:
+            raise ValueError("the gather kernel takes at most 16 ranks")
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.storage.zero_()                       # flag block: epochs, ticket and status start at zero
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)                  # nobody signals into a block that is not zeroed yet
+        self.used = self.ALIGN
+        self.buffers = {}
+
+    @property
+    def flag_ptrs(self):
+        return self.ptrs
+
+    def output(self, key, m, n):
+        """The `[m, n]` FP16 buffer registered under `key` (allocated on first use): its local
+        tensor and the per-rank device addresses."""
+        hit = self.buffers.get((key, m, n))
+        if hit is not None:
+            return hit
+        size = -(-(m * n * 2) // self.ALIGN) * self.ALIGN
+        if self.used + size > self.bytes:
+            raise RuntimeError(f"PeerArena of {self.bytes} bytes is full ({self.used} used, {size} more requested)")
+        local = self.storage[self.used:self.used + m * n * 2].view(torch.float16).view(m, n)
+        entry = (local, [p + self.used for p in self.ptrs])
+        self.used += size
+        self.buffers[(key, m, n)] = entry
+        return entry
+
+    def status(self):
+        """Sticky status word of this rank's flag block (synchronizes; bit 2 = a peer's flag did
+        not arrive within the wait limit)."""
+        return _native.gather_status(self.ptrs[self.rank])
+
+
 class ColumnShardedLinear(torch.nn.Module):
     """This rank's row slice of a QuantizedLinear plus the optional gather of outputs."""
 
@@ -43,6 +113,15 @@ class ColumnShardedLinear(torch.nn.Module):
         self.process_group = process_group
         self.rows = (start, stop)
         self.rows_per_rank = shard_rows(out_features, world_size, 0)[1]
+        self.arena = None
+        self._calls = 0
+
+    def attach_arena(self, arena):
+        """Gather through peer stores into `arena` (a PeerArena of the same ranks) from now on."""
+        if arena.world != self.world_size or arena.rank != self.rank:
+            raise ValueError("arena belongs to another group")
+        self.arena = arena
+        return self
 
     @classmethod
     def from_float(cls, weight, bias=None, *, rank, world_size, process_group=None, group_size=64,
@@ -80,12 +159,29 @@ class ColumnShardedLinear(torch.nn.Module):
     def forward(self, x, gather=False, compute=None):
         """Local slice `[M, n_local]`, or the full `[M, N]` on every rank when `gather`.
         `compute` replaces the local layer's forward (tests of the exchange logic)."""
+        if gather and self.arena is not None and compute is None and self.world_size > 1:
+            return self._forward_peer_gather(x)
         run = compute if compute is not None else self.local
         if run is None:
             y = x.new_empty((x.shape[0], 0))
         else:
             y = run(x)
         return self.gather(y) if gather else y
+
+    def _forward_peer_gather(self, x):
+        """Projection into this rank's columns of the symmetric `[M, N]` buffer, then one
+        `b2_w4a16_gather` launch.  Two buffers per batch size are used in turn, so a peer that runs
+        ahead writes the next call's slice into the other buffer while this rank still reads this one
+        (a captured graph replays the buffer it was captured with: see include/b2_w4a16.h)."""
+        m = x.shape[0]
+        full, ptrs = self.arena.output((id(self), self._calls & 1), m, self.out_features)
+        self._calls += 1
+        start, stop = self.rows
+        if self.local is not None and m > 0:
+            self.local.forward_into(x, full[:, start:stop])
+        if m > 0:
+            _native.gather(ptrs, self.arena.flag_ptrs, self.rank, m, self.out_features, start, stop - start)
+        return full
 
     def gather(self, y_local):
         """All-gather of the per-rank slices into `[M, N]` (same result on every rank)."""

@@ -224,6 +224,32 @@ int b2_w4a16_plan(int64_t m, int64_t n, int64_t k, int* route, int* k_splits, in
  * area, workspace smaller than b2_w4a16_workspace_bytes()) is reduced. */
 int b2_w4a16_set_gemm_shape(int shape, int k_splits);
 
+/* Multi-GPU: all-gather of the column slices of an [M, N] FP16 output over NVLink.  No counterpart in
+ * the reference, which is single-GPU; it is the collective step of the column-sharded layer (each rank
+ * owns the output columns of its rows of W).  Every rank has its own copy of the [m, ld] buffer in memory
+ * that all peers can write (peer-mapped / symmetric memory) and has written its slice
+ * [col0, col0 + cols) into its own copy - the projection stores there directly.  The call pushes that
+ * slice into every peer's copy with plain stores, then exchanges epoch flags: when the kernel ends, the
+ * local copy holds every rank's slice.  One launch; nothing reads remote memory.
+ *   y_ranks[q], flag_blocks[q]  HOST arrays of `world` device pointers as mapped into this process
+ *                               (entry [rank] is this rank's own); a flag block is
+ *                               B2_GATHER_FLAG_BYTES of zero-initialised memory, one per rank and
+ *                               process, shared by every gathered layer; all ranks must issue the same
+ *                               sequence of gathers.
+ * The wait for the peers is bounded (five seconds by default, b2_w4a16_gather_wait_limit): if a
+ * peer's flag does not arrive, bit 2 of the flag block's status word is set (b2_w4a16_gather_status
+ * reads it, synchronizing) and the kernel returns.  Reuse of one buffer: a peer may start writing the
+ * next call's slice as soon as it has seen this rank's flag, so between two gathers into the SAME
+ * buffer a rank must issue at least one other gather (or alternate two buffers). */
+#define B2_GATHER_FLAG_BYTES 128
+int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int rank, int world, int64_t m, int64_t ld,
+                    int64_t col0, int64_t cols, void* stream);
+int b2_w4a16_gather_status(const void* flag_block, void* stream, unsigned* status_host);
+int b2_w4a16_gather_wait_limit(int64_t microseconds);      /* <= 0 restores the default */
+
+/* Launches an empty kernel on `stream`: the floor of one graph node, for benchmarks. */
+int b2_w4a16_noop(void* stream);
+
 /* Test hooks, no counterpart in the reference.  wait_limit: polls after which a kernel's bounded
  * wait for a weight copy gives up (<= 0 restores the default, about a million).  skip_copy >= 0: the
  * NEXT decode-kernel launch (tile or streaming) arms the barrier of that copy of its first CTA but does
