@@ -94,14 +94,18 @@ gather_push_wait_kernel(const GatherArgs a) {
     if (threadIdx.x < a.world && int(threadIdx.x) != a.rank) {
         const int q = threadIdx.x;
         st_release_sys(a.flags[q] + a.rank, epoch);              // my slice has landed in q's buffer
-        // Bounded by the clock and by a poll count (a poll takes at least the 64 ns sleep, so the count
-        // alone ends the loop even if the timer stood still).
+        // Bounded by the clock and by a poll count: the first polls come back to back (a flag that is a
+        // microsecond away should not cost a sleep), later ones sleep 100 ns each, so the count alone ends
+        // the loop even if the timer stood still.
         const unsigned long long t0 = global_ns();
         bool arrived = false;
-        for (long long i = 0; i < a.wait_ns && !arrived; ++i) {
+        for (long long i = 0; i < a.wait_ns + 4096 && !arrived; ++i) {
             arrived = int(ld_acquire_sys(mine + q) - epoch) >= 0;
-            if (arrived || global_ns() - t0 > (unsigned long long)a.wait_ns) break;
-            __nanosleep(64);
+            if (arrived) break;
+            if (i >= 4096) {
+                if (global_ns() - t0 > (unsigned long long)a.wait_ns) break;
+                __nanosleep(100);
+            }
         }
         if (!arrived) atomicOr(mine + kGatherStatusWord, kStatusPeerTimeout);
     }
