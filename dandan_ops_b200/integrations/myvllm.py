@@ -52,10 +52,50 @@ def convert_signed_int4(weight, scales, in_features, source_group_size=SOURCE_GR
     return words, steps, zeros
 
 
-class EngineQuantLinear(nn.Module):
-    """Projection adapter: any leading dimensions in, same leading dimensions out."""
+def _validate_config(config):
+    """The engine configuration the bridge accepts (dandan_ops/integrations/myvllm.py:48-51)."""
+    if (config.canonical_weight_dtype != "int4" or config.activation_dtype != "fp16"
+            or config.group_size != SOURCE_GROUP or not config.symmetric):
+        raise ValueError("myvllm dandan adapter requires symmetric INT4, FP16 activation, group_size=128")
 
-    def __init__(self, packed_weight, scales, in_features, out_features, bias=None):
+
+def _is_config(obj):
+    return all(hasattr(obj, a) for a in ("canonical_weight_dtype", "activation_dtype", "group_size", "symmetric"))
+
+
+def engine_packer():
+    """The engine's own signed-INT4 group-128 packer as `linear -> (packed uint8, FP32 scales)`.  The engine
+    (`mini_engine`) is an external checkout; it is imported only here, on demand, as the reference does."""
+    try:
+        from mini_engine.quantization.backends import Int4WeightOnlyBackend
+    except ImportError as exc:
+        raise ImportError("the (model, config) form needs the engine's quantizer (mini_engine) on the path; "
+                          "pass pack_linear=... to use another packer") from exc
+    backend = Int4WeightOnlyBackend(SOURCE_GROUP)
+
+    def pack(linear):
+        source = backend.pack(linear.weight)
+        return source.weight, source.scale
+    return pack
+
+
+class EngineQuantLinear(nn.Module):
+    """Projection adapter: any leading dimensions in, same leading dimensions out.
+
+    Two call shapes: `EngineQuantLinear(packed_weight, scales, in_features, out_features, bias=None)` from the
+    engine's packed tensors, or the reference's `EngineQuantLinear(linear, config)` (an `nn.Linear` on CUDA in
+    FP16 plus the engine's quantization config; needs the engine's packer, see `engine_packer`)."""
+
+    def __init__(self, packed_weight, scales, in_features=None, out_features=None, bias=None, pack_linear=None):
+        if isinstance(packed_weight, nn.Linear):
+            linear, config = packed_weight, scales
+            _validate_config(config)
+            if linear.weight.device.type != "cuda" or linear.weight.dtype != torch.float16:
+                raise ValueError("source model must be CUDA FP16")
+            packed_weight, scales = (pack_linear or engine_packer())(linear)
+            in_features, out_features, bias = linear.in_features, linear.out_features, linear.bias
+        elif _is_config(scales):
+            raise TypeError("source projection must be nn.Linear")
         super().__init__()
         words, steps, zeros = convert_signed_int4(packed_weight, scales, in_features)
         if words.shape[0] != out_features:
@@ -79,13 +119,20 @@ class EngineQuantLinear(nn.Module):
         return y.reshape(*x.shape[:-1], self.out_features)
 
 
-def install_int4_projections(model, pack_linear, prefix="model.layers."):
+def install_int4_projections(model, pack_linear, prefix="model.layers.", *, packer=None):
     """Replace every `nn.Linear` under `prefix` by an EngineQuantLinear.
 
-    `pack_linear(linear) -> (packed uint8, FP32 scales)` is the engine's own signed-INT4
-    group-128 packer.  All replacements are prepared before the model is touched, so a
-    failure leaves it unchanged.  Returns the report the reference attaches to the model
+    The second argument is either `pack_linear(linear) -> (packed uint8, FP32 scales)`, the engine's
+    signed-INT4 group-128 packer, or - the reference's call shape, `install_int4_projections(model, config)` -
+    the engine's quantization config, which is validated as the reference validates it and then uses
+    `packer` or the engine's own packer (`engine_packer()`).  All replacements are prepared before the model
+    is touched, so a failure leaves it unchanged.  Returns the report the reference attaches to the model
     (dandan_ops/integrations/myvllm.py:87-119)."""
+    if _is_config(pack_linear):
+        _validate_config(pack_linear)
+        pack_linear = packer
+    elif not callable(pack_linear):
+        raise TypeError("the second argument is the engine's quantization config or a packer callable")
     if getattr(model, "quantization_report", None) is not None:
         raise ValueError("model is already quantized; reload floating weights")
     if getattr(model, "projection_fusion_enabled", False):
@@ -98,6 +145,8 @@ def install_int4_projections(model, pack_linear, prefix="model.layers."):
     for name, linear in selected:
         if linear.weight.device.type != "cuda" or linear.weight.dtype != torch.float16:
             raise ValueError("source model must be CUDA FP16")
+        if pack_linear is None:
+            pack_linear = engine_packer()
         packed, scales = pack_linear(linear)
         prepared.append((name, EngineQuantLinear(packed, scales, linear.in_features, linear.out_features,
                                                  bias=linear.bias)))

@@ -101,3 +101,51 @@ def test_engine_linear_keeps_leading_dims_and_installs_into_a_model():
         layer(x.bfloat16())
     o = toy.model.layers[1].o_proj
     assert o.op.bias is not None and o(torch.randn(5, 384, dtype=torch.float16, device="cuda")).shape == (5, 256)
+
+
+def test_reference_call_shape_with_a_config_object():
+    """`install_int4_projections(model, config)` and `EngineQuantLinear(linear, config)`, the reference's
+    signatures (dandan_ops/integrations/myvllm.py:54-66, 87): the config is validated with the reference's
+    wording; without the external engine on the path the packer must be given, else ImportError."""
+    from types import SimpleNamespace
+
+    good = SimpleNamespace(canonical_weight_dtype="int4", activation_dtype="fp16", group_size=128, symmetric=True)
+    model = torch.nn.Module()
+    model.model = torch.nn.Module()
+    model.model.layers = torch.nn.ModuleList([torch.nn.Linear(128, 16, bias=False)])
+    for bad in (dict(group_size=64), dict(symmetric=False), dict(activation_dtype="bf16"), dict(canonical_weight_dtype="int8")):
+        cfg = SimpleNamespace(**{**vars(good), **bad})
+        with pytest.raises(ValueError, match="symmetric INT4, FP16 activation, group_size=128"):
+            install_int4_projections(model, cfg)
+        with pytest.raises(ValueError, match="symmetric INT4, FP16 activation, group_size=128"):
+            EngineQuantLinear(model.model.layers[0], cfg)
+    with pytest.raises(ValueError, match="CUDA FP16"):                 # a CPU model is refused before any packing
+        install_int4_projections(model, good, packer=lambda lin: signed_pack(lin.weight.detach())[:2])
+    with pytest.raises(ValueError, match="CUDA FP16"):
+        EngineQuantLinear(model.model.layers[0], good)
+    with pytest.raises(TypeError, match="config or a packer"):
+        install_int4_projections(model, 3)
+    with pytest.raises(TypeError, match="nn.Linear"):
+        EngineQuantLinear(torch.zeros(1), good)
+    assert getattr(model, "quantization_report", None) is None and isinstance(model.model.layers[0], torch.nn.Linear)
+
+
+@pytest.mark.gpu
+def test_reference_call_shape_on_a_gpu_model():
+    from types import SimpleNamespace
+
+    good = SimpleNamespace(canonical_weight_dtype="int4", activation_dtype="fp16", group_size=128, symmetric=True)
+    torch.manual_seed(9)
+    model = torch.nn.Module()
+    model.model = torch.nn.Module()
+    model.model.layers = torch.nn.ModuleList([torch.nn.Linear(256, 64, bias=True)])
+    model = model.half().cuda()
+    with pytest.raises(ImportError, match="mini_engine"):               # the external engine is not installed here
+        install_int4_projections(model, good)
+    assert isinstance(model.model.layers[0], torch.nn.Linear)           # untouched after the failure
+    pack = lambda lin: signed_pack(lin.weight.detach())[:2]            # noqa: E731
+    single = EngineQuantLinear(model.model.layers[0], good, pack_linear=pack)
+    report = install_int4_projections(model, good, packer=pack)
+    assert report["replaced_layers"] == ["model.layers.0"] and report["source_group_size"] == 128
+    x = torch.randn(3, 256, dtype=torch.float16, device="cuda")
+    assert torch.equal(model.model.layers[0](x), single(x))
