@@ -273,6 +273,9 @@ def status(device=None):
             word = ctypes.c_uint(0)
             _check(lib.b2_w4a16_status(ws.data_ptr(), _stream(), ctypes.byref(word)))
             result |= int(word.value)
+    from . import ops as _ops
+    if _ops.SHIM_LOADED:          # the workspaces the C++ operator library handed out
+        result |= int(torch.ops.dandan_ops.w4a16_workspace_status())
     return result
 
 

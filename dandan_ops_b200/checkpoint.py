@@ -5,12 +5,17 @@
   optional `<prefix>bias`, `<prefix>_extra_state`; dandan_ops/quantized_linear.py:105-146) go
   straight into engine layers and come back unchanged, tensor for tensor.
 * `ImageCache`: the device-native weight image of a layer (what `b2_w4a16_repack` builds) kept on
-  disk under a key that is a hash of the layer's state, so that a server restart maps the file
-  instead of repacking.  The file is the image bytes behind a 64-byte header.
+  disk under a key that is a hash of the layer's state.  `ImageCache.load_layer(state)` is the restart
+  path: it hashes the checkpoint tensors while they are still on the host, builds the layer without
+  repacking, reads the image file (header with a CRC-32 of the image bytes, verified) and copies it to
+  the device; only a miss repacks.  `attach(layer)` serves layers that already exist on the device (it
+  has to copy their state back to hash it, so it saves nothing over the repack kernel and exists for
+  filling the cache).
 """
 import hashlib
 import os
 import struct
+import zlib
 
 import numpy as np
 import torch
@@ -61,7 +66,7 @@ def export_int4_layers(layers):
 # ---------------------------------------------------------------------------------------------
 IMAGE_MAGIC = b"B2W4IMG1"
 IMAGE_LAYOUT = 1            # 16 x 256 blocks of 2336 bytes: codes, FP32 steps, 4-bit zero points
-_HEADER = struct.Struct("<8sIIqqq24x")        # magic, layout, format version, N, K, image bytes; 64 bytes
+_HEADER = struct.Struct("<8sIIqqqI20x")       # magic, layout, format version, N, K, image bytes, CRC-32 of the image; 64 bytes
 
 
 def state_digest(packed_weight, scales, zeros, in_features):
@@ -78,7 +83,7 @@ def write_image_file(path, image_bytes, n, k):
     data = bytes(image_bytes) if not isinstance(image_bytes, np.ndarray) else image_bytes.tobytes()
     tmp = f"{path}.tmp{os.getpid()}"
     with open(tmp, "wb") as f:
-        f.write(_HEADER.pack(IMAGE_MAGIC, IMAGE_LAYOUT, FORMAT_VERSION, n, k, len(data)))
+        f.write(_HEADER.pack(IMAGE_MAGIC, IMAGE_LAYOUT, FORMAT_VERSION, n, k, len(data), zlib.crc32(data)))
         f.write(data)
     os.replace(tmp, path)          # readers never see a partial file
 
@@ -90,14 +95,16 @@ def read_image_file(path, n, k, expected_bytes):
             head = f.read(_HEADER.size)
             if len(head) != _HEADER.size:
                 return None
-            magic, layout, version, fn, fk, nbytes = _HEADER.unpack(head)
+            magic, layout, version, fn, fk, nbytes, crc = _HEADER.unpack(head)
             if (magic, layout, version, fn, fk, nbytes) != (IMAGE_MAGIC, IMAGE_LAYOUT, FORMAT_VERSION, n, k,
                                                             expected_bytes):
                 return None
             data = np.fromfile(f, dtype=np.uint8, count=nbytes)
     except OSError:
         return None
-    return data if data.size == expected_bytes else None
+    if data.size != expected_bytes or zlib.crc32(data.tobytes()) != crc:      # truncated or damaged file: a miss
+        return None
+    return data
 
 
 class ImageCache:
@@ -119,6 +126,30 @@ class ImageCache:
         image = layer._native_image()
         write_image_file(path, image.cpu().numpy(), layer.out_features, layer.in_features)
         return path
+
+    def load_layer(self, state, device="cuda", backend="auto"):
+        """(layer on `device`, hit) from a per-layer state dict in the reference's format whose tensors
+        are on the HOST: the restart path.  The key is hashed from the host tensors, the layer is built
+        without its image (`defer_image=True`), and on a hit the image comes from the file - no repack
+        kernel, no device-to-host copy.  On a miss the image is built on the device and stored."""
+        meta = state.get("_extra_state")
+        if not isinstance(meta, dict) or meta.get("format_version") != FORMAT_VERSION:
+            raise ValueError("missing or unsupported INT4 format_version")
+        n, k = (int(v) for v in meta["original_shape"])
+        path = os.path.join(self.directory, state_digest(state["packed_weight"], state["scales"], state["zeros"], k) + ".b2img")
+        bias = state.get("bias")
+        layer = QuantizedLinear(state["packed_weight"].to(device), state["scales"].to(device), state["zeros"].to(device),
+                                in_features=k, group_size=meta["group_size"], bias=None if bias is None else bias.to(device),
+                                backend=backend, defer_image=True)
+        layer.set_extra_state(meta)
+        data = read_image_file(path, n, k, _native.native_bytes(n, k))
+        if data is None:
+            self.misses += 1
+            write_image_file(path, layer._native_image().cpu().numpy(), n, k)
+            return layer, False
+        self.hits += 1
+        layer.attach_native_image(_native.image_from_host(torch.from_numpy(data), layer.packed_weight.device))
+        return layer, True
 
     def attach(self, layer):
         """Give a CUDA layer its image from the cache (True) or build and store it (False)."""

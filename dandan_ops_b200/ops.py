@@ -10,7 +10,6 @@ checks and their messages follow `check_w4a16` (`dandan_ops/csrc/gemm_checks.h:6
 import torch
 
 from . import _native
-from .quantized_linear import _image_for
 
 _INT_MAX = 2**31 - 1
 _SCHEMA = "(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size) -> Tensor"
@@ -46,6 +45,7 @@ def check_w4a16(x, packed, scales, zeros, group_size):
 def _run(x, packed, scales, zeros, group_size, rule):
     check_w4a16(x, packed, scales, zeros, group_size)
     rule(x, group_size)
+    from .quantized_linear import _image_for
     image = _image_for(packed, scales, zeros, x.shape[1])
     return _native.linear(x, image, packed.shape[0], x.shape[1])
 
@@ -71,11 +71,28 @@ _OPS = {"w4a16_gemv": _rule_gemv, "w4a16_small": _rule_small,
         "w4a16_tensorcore": _rule_any, "w4a16_gemm": _rule_naive}
 
 
+SHIM_LOADED = False      # True when the ops come from the C++ operator library (lib/dandan_ops_b200_C.so)
+
+
 def register():
-    """Define the ops once per process (no-op if the names already exist)."""
-    global _registered, _library
+    """Define the ops once per process (no-op if the names already exist).
+
+    The C++ operator library (csrc/torch_shim/shim.cpp, built by `dandan_ops_b200.build.build_shim`) is loaded
+    with `torch.ops.load_library`, as the reference loads its `_C` module (dandan_ops/_extension.py:34); it
+    registers the same names with TORCH_LIBRARY.  Where that file has not been built, the names are defined
+    from Python over the ctypes binding instead - the same C-ABI kernels either way."""
+    global _registered, _library, SHIM_LOADED
     if _registered:
         return
+    from . import build as _build
+    if _build.SHIM_PATH.is_file() and _build.LIB_PATH.is_file():
+        try:
+            torch.ops.load_library(str(_build.SHIM_PATH))
+            SHIM_LOADED = True
+            _registered = True
+            return
+        except OSError:           # stale binary for another torch: fall through to the Python definitions
+            pass
     _library = torch.library.Library("dandan_ops", "FRAGMENT")
     for name, rule in _OPS.items():
         _library.define(name + _SCHEMA)

@@ -24,6 +24,7 @@ import weakref
 import torch
 
 from . import _native
+from . import ops as _ops_module
 from .quantization import CUDA_ONLY, pack_int4, quantize_int4, validate_int4_state
 
 BACKENDS = ("auto", "cuda", "gemv", "small", "tensorcore", "naive", "reference")
@@ -86,6 +87,8 @@ def _engine(x, image, rows, in_features, bias16):
     FP16 first and add the FP16 bias afterwards, as the reference's `y + bias.to(y.dtype)` does."""
     if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < in_features):
         x = x.contiguous()
+    if _ops_module.SHIM_LOADED:       # C++ operator library: output, workspace and launch without a ctypes round trip
+        return torch.ops.dandan_ops.w4a16_linear_image(x, image, rows, in_features, bias16, 0)
     return _native.linear(x, image, rows, in_features, bias=bias16)
 
 
@@ -116,7 +119,9 @@ class QuantizedLinear(torch.nn.Module):
     """
 
     def __init__(self, packed_weight, scales, zeros, *, in_features, group_size=64, bias=None,
-                 backend="auto"):
+                 backend="auto", defer_image=False):
+        """`defer_image=True` (an addition to the reference's signature) skips the eager build of the
+        device-native image: for loaders that attach a prebuilt one (`checkpoint.ImageCache.load_layer`)."""
         super().__init__()
         if backend not in BACKENDS:
             raise ValueError("invalid quantized backend")
@@ -137,7 +142,7 @@ class QuantizedLinear(torch.nn.Module):
         self._checked_key = None
         self._checked_device = None
         self.eval()
-        if self.packed_weight.is_cuda and group_size == 64:
+        if self.packed_weight.is_cuda and group_size == 64 and not defer_image:
             self._native_image()
 
     # -- construction ----------------------------------------------------------------------

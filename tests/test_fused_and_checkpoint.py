@@ -150,6 +150,29 @@ def test_image_cache_hit_equals_repack(tmp_path):
 
 
 @pytest.mark.gpu
+def test_image_cache_restart_path_skips_the_repack_and_rejects_damaged_files(tmp_path):
+    """`load_layer` on a host state dict: first a miss (repack + store), then a hit that launches no
+    repack kernel; a file with a flipped byte fails its CRC and counts as a miss."""
+    cache = checkpoint.ImageCache(tmp_path)
+    state = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in _layer(300, 1032, 6, bias=True).state_dict().items()}
+    first, hit = cache.load_layer(state)
+    assert hit is False and cache.misses == 1
+    before = _native.launch_count()
+    second, hit = cache.load_layer(state)
+    assert hit is True and _native.launch_count() == before             # nothing launched: no repack
+    assert torch.equal(second._native_image(), first._native_image())
+    x = torch.randn(4, 1032).half().cuda()
+    assert torch.equal(second(x), first(x)) and second.bias is not None
+    (path,) = list(tmp_path.iterdir())
+    raw = bytearray(path.read_bytes())
+    raw[64 + 1000] ^= 0x10
+    path.write_bytes(bytes(raw))
+    third, hit = cache.load_layer(state)
+    assert hit is False and torch.equal(third._native_image(), first._native_image())    # rebuilt, file rewritten
+    assert cache.load_layer(state)[1] is True
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("m", [1, 3, 8, 16, 33, 64, 65, 300, 1000])
 @pytest.mark.parametrize("rows,k,bias", [(1536, 1024, False), (3072, 1024, True), (1000, 4096, True), (8, 200, False),
                                           (12288, 4096, False), (512, 3072, True)])

@@ -225,3 +225,24 @@ def test_gemm_cost_model_picks_pair_kernels():
     assert _native.plan(48, 6144, 1024)["route"] == "b200_stream"       # small layer: streaming kernel up to 64 rows
     split = _native.plan(256, 4096, 28672)                              # 16 tiles, 112 blocks of K: four CTAs per tile
     assert split["k_splits"] == 4 and split["grid"] == 2 * 16 * 4
+
+
+def test_operator_library_registers_the_reference_op_names():
+    """The C++ operator library (TORCH_LIBRARY over the C ABI) builds without a GPU, loads with
+    torch.ops.load_library and defines the reference's native op surface
+    (dandan_ops/csrc/operators.cu:259-278, dandan_ops/csrc/hgemm.cu:89-98)."""
+    import torch
+
+    from dandan_ops_b200 import build as b2build
+    from dandan_ops_b200 import ops as b2ops
+
+    path = b2build.build_shim()
+    assert path.is_file()
+    import dandan_ops_b200  # noqa: F401  (registers on import)
+    for name in ("w4a16_gemv", "w4a16_small", "w4a16_tensorcore", "w4a16_gemm", "w4a16_contract_version"):
+        assert hasattr(torch.ops.dandan_ops, name)
+    assert torch.ops.dandan_ops.w4a16_contract_version() == 2
+    if b2ops.SHIM_LOADED:
+        assert hasattr(torch.ops.dandan_ops, "w4a16_linear_image")
+        schema = str(torch.ops.dandan_ops.w4a16_small.default._schema)
+        assert "Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size" in schema
