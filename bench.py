@@ -349,6 +349,13 @@ def run_gpu(args, rank, world, local_rank):
         sync_all()
         graph = capture(one_step, stream)
         proj_graph = graph if not gather_on else capture(proj_step, stream)
+
+        def gather_step():                             # the exchange alone: every linear's gather launch, no projection
+            for c in calls:
+                sl = c["sharded"]
+                full, ptrs = sl.arena.output((id(sl), 0), c["m"], c["n_full"])
+                _native.gather(ptrs, sl.arena.flag_ptrs, rank, c["m"], c["n_full"], sl.rows[0], sl.rows[1] - sl.rows[0])
+        gather_graph = capture(gather_step, stream) if gather_on else None
         floor_graph = capture(lambda: [_native.noop() for _ in range(launches_per_step)], stream)
         warm = max(args.warmup, 3)
         for _ in range(warm):
@@ -360,6 +367,7 @@ def run_gpu(args, rank, world, local_rank):
             gpu_ms = time_graph(graph, stream, sync_all, args.steps)
             clocks.hold_load(proj_graph.replay, stream.synchronize, first + 3, 2.0)
         proj_ms = gpu_ms if not gather_on else time_graph(proj_graph, stream, sync_all, args.steps)
+        gather_ms = time_graph(gather_graph, stream, sync_all, args.steps) if gather_on else 0.0
         floor_ms = time_graph(floor_graph, stream, sync_all, max(args.steps, 20))
 
         # ---- end to end: x starts in pinned host memory, y ends there, every step -----------------
@@ -423,12 +431,13 @@ def run_gpu(args, rank, world, local_rank):
 
         parity = parity_check([c for c in calls if c["li"] == 0], x_dev, run_call, rank, world, gather_on)
 
-    times = torch.tensor([gpu_ms, e2e_ms, e2e_eager_ms, proj_ms, floor_ms], dtype=torch.float64, device=device)
+    times = torch.tensor([gpu_ms, e2e_ms, e2e_eager_ms, proj_ms, floor_ms, gather_ms], dtype=torch.float64, device=device)
     bytes_all = torch.tensor([step_weight_bytes, step_alg_bytes], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(bytes_all, op=dist.ReduceOp.SUM)
-    ms_per_step, e2e_ms_per_step, e2e_eager_ms_per_step, proj_ms_per_step, floor_ms_per_step = (float(v) for v in times.cpu())
+    ms_per_step, e2e_ms_per_step, e2e_eager_ms_per_step, proj_ms_per_step, floor_ms_per_step, gather_ms_per_step = (
+        float(v) for v in times.cpu())
     weight_total, alg_total = (float(v) for v in bytes_all.cpu())
     status = _native.status() | (arena.status() if arena is not None else 0)
 
@@ -507,6 +516,9 @@ def run_gpu(args, rank, world, local_rank):
             result["projection_only"] = {"ms_per_step": round(proj_ms_per_step, 4),
                                          "value": round(weight_total / (proj_ms_per_step * 1e-3) / 1e9, 2), "unit": "GB/s",
                                          "note": "the same step without the gather launches"}
+            result["gather_only"] = {"ms_per_step": round(gather_ms_per_step, 4),
+                                     "us_per_gather": round(gather_ms_per_step * 1e3 / len(calls), 2),
+                                     "note": "the gather launches of the step alone, ranks in lockstep (no projection between them)"}
         print(json.dumps(result))
     if world > 1:
         dist.barrier()

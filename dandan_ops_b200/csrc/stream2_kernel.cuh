@@ -10,7 +10,10 @@
 //     scheduler a warp takes twice as long per block, so two slots cover the same latency;
 //   * the first weight copies are requested before anything else happens in the CTA;
 //   * x is staged in phases of 2048 / MT columns into two buffers, the next phase fetched with
-//     cp.async while the current one is used: one block-wide barrier per phase, nobody waits for x;
+//     cp.async while the current one is used.  No block-wide barrier: each buffer has a "full"
+//     mbarrier (every thread's copies have landed) and an "empty" one (every warp is done with it),
+//     and a warp stages its share of the next phase half-way through the current one - by then the
+//     slowest warp has normally left the previous phase, so nobody waits for anybody;
 //   * a range that ends inside a row group starts with that trailing fragment: its partial tile
 //     and ticket are out of the way early, and the last thing a CTA does is a plain store of a
 //     whole row group instead of the fence / ticket / re-read of a split one;
@@ -25,8 +28,13 @@ namespace b2 {
 __host__ __device__ constexpr int s2_stages(int w) { return 64 / w; }
 __host__ __device__ constexpr int s2_phase_blocks(int mt) { return 8 / mt; }
 __host__ __device__ constexpr int s2_xbuf_bytes(int mt) { return s2_phase_blocks(mt) * 4 * stream_x_chunk_bytes(mt * 8); }
+constexpr int kS2BarBytes = 64 * 8 + 64;      // 64 ring barriers + full[2], empty[2] of the x buffers (padded)
 __host__ __device__ constexpr int s2_smem_bytes(int mt) {
-    return 64 * 8 + 64 * kBlockBytes + 2 * s2_xbuf_bytes(mt);
+    return kS2BarBytes + 64 * kBlockBytes + 2 * s2_xbuf_bytes(mt);
+}
+// Arrives on `bar` once all cp.async copies this thread has issued so far have landed.
+__device__ __forceinline__ void mbar_arrive_after_copies(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 template <int MT, bool XVEC, int W>
@@ -37,7 +45,7 @@ w4a16_stream2_kernel(const StreamArgs a) {
     constexpr int PB = s2_phase_blocks(MT);
     constexpr int kChunk = stream_x_chunk_bytes(MP);
     constexpr int kXBuf = s2_xbuf_bytes(MT);
-    constexpr int kBarBytes = W * S * 8, kRingBytes = W * S * kBlockBytes;
+    constexpr int kBarBytes = kS2BarBytes, kRingBytes = W * S * kBlockBytes;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -94,6 +102,17 @@ w4a16_stream2_kernel(const StreamArgs a) {
             fbase = a.native + (long long)(fgrp * W + warp) * kBlockBytes;
         }
     };
+    // x buffers: full[b] completes when every thread's copies into buffer b have landed (two arrivals per
+    // thread: one for its plain stores, one that fires after its cp.async copies), empty[b] when every
+    // warp has finished the phase that used it.
+    const uint32_t xfull = smem_u32(smem) + 64 * 8, xempty = xfull + 16;
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(xfull + b * 8, 2 * W * 32);
+            mbar_init(xempty + b * 8, W);
+        }
+    }
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < S; ++s) mbar_init(bar0 + s * 8, 1);
@@ -102,7 +121,7 @@ w4a16_stream2_kernel(const StreamArgs a) {
 #pragma unroll
     for (int s = 0; s < S; ++s)
         if (fetch_left > 0) request(s);
-    __syncwarp();
+    __syncthreads();                                  // the x barriers exist before anybody arrives on them
 
     // ---- x: resident when all of K fits in the two buffers, else double-buffered phases -----------
     const bool resident = a.kb <= 2 * PB;
@@ -113,6 +132,8 @@ w4a16_stream2_kernel(const StreamArgs a) {
     int kbi = ps - grp * a.kb;
     if (resident) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols);
     else stage_x<MT, XVEC, W, false>(xs, a, kbi * kBlockCols, min(PB, min(a.kb - kbi, pend - ps)) * kBlockCols);
+    mbar_arrive(xfull);
+    mbar_arrive_after_copies(xfull);
 
     float acc[MT][4];
     int stage = 0;
@@ -120,8 +141,7 @@ w4a16_stream2_kernel(const StreamArgs a) {
     bool failed = false;
     int k_lo = kbi;                                   // first column block of the current segment
     bool seg_start = true;
-    int buf = 0;
-    bool first_phase = true;
+    int phase = 0;                                    // phase j uses buffer j & 1 for the (j >> 1)-th time
 
     // Moves (ps, pend, part, grp, kbi) from a phase of `cnt` blocks to the next one; ps = -1 at the end.
     auto advance = [&](int& ps_, int& pend_, int& part_, int& grp_, int& kbi_, int cnt) {
@@ -136,18 +156,29 @@ w4a16_stream2_kernel(const StreamArgs a) {
 
     while (ps >= 0) {
         const int cnt = min(PB, min(a.kb - kbi, pend - ps));
-        if (!resident || first_phase) {
-            stage_wait();
-            __syncthreads();                          // this phase's x has landed; everyone is done with the other buffer
-            if (!resident) {
-                int ns = ps, npend = pend, npart = part, ngrp = grp, nkbi = kbi;
-                advance(ns, npend, npart, ngrp, nkbi, cnt);
-                if (ns >= 0)
-                    stage_x<MT, XVEC, W, false>(xs + (buf ^ 1) * kXBuf, a, nkbi * kBlockCols,
-                                                min(PB, min(a.kb - nkbi, npend - ns)) * kBlockCols);
+        const int buf = phase & 1;
+        if (!resident || phase == 0) {
+            if (!mbar_wait(xfull + buf * 8, (phase >> 1) & 1, a.wait_limit) && !failed) {
+                failed = true;
+                if (lane == 0) atomicOr(a.status, kStatusCopyTimeout);
             }
-            first_phase = false;
         }
+        // Half-way through the phase every warp stages its share of the next one into the other buffer,
+        // once all warps have left the phase that used that buffer before.
+        auto prefetch_next = [&]() {
+            int ns = ps, npend = pend, npart = part, ngrp = grp, nkbi = kbi;
+            advance(ns, npend, npart, ngrp, nkbi, cnt);
+            if (ns < 0) return;
+            if (phase >= 1 && !mbar_wait(xempty + (buf ^ 1) * 8, ((phase - 1) >> 1) & 1, a.wait_limit) && !failed) {
+                failed = true;
+                if (lane == 0) atomicOr(a.status, kStatusCopyTimeout);
+            }
+            stage_x<MT, XVEC, W, false>(xs + (buf ^ 1) * kXBuf, a, nkbi * kBlockCols,
+                                        min(PB, min(a.kb - nkbi, npend - ns)) * kBlockCols);
+            mbar_arrive(xfull + (buf ^ 1) * 8);
+            mbar_arrive_after_copies(xfull + (buf ^ 1) * 8);
+        };
+        const int half = cnt >> 1;
         if (seg_start) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
@@ -158,13 +189,15 @@ w4a16_stream2_kernel(const StreamArgs a) {
         }
         const int nt = grp * W + warp;
         const bool active = nt < a.n16;
-        if (active && !failed) {
+        {
             const uint8_t* xbase = resident ? xs + (kbi * 4 + t) * kChunk + g * 144 : xs + buf * kXBuf + t * kChunk + g * 144;
             for (int kbl = 0; kbl < cnt; ++kbl) {
+                if (kbl == half && !resident) prefetch_next();
+                if (!active || failed) continue;
                 if (!mbar_wait(bar0 + stage * 8, parity, a.wait_limit)) {
                     failed = true;
                     if (lane == 0) atomicOr(a.status, kStatusCopyTimeout);
-                    break;
+                    continue;
                 }
                 const uint8_t* slot = ring + stage * kBlockBytes;
                 const float2 step = *reinterpret_cast<const float2*>(slot + kStepOffset + lane * 8);
@@ -210,6 +243,10 @@ w4a16_stream2_kernel(const StreamArgs a) {
             }
         }
 
+        if (!resident) {
+            __syncwarp();                             // every lane is done with this phase's x
+            if (lane == 0) mbar_arrive(xempty + buf * 8);
+        }
         const bool seg_end = (kbi + cnt == a.kb) || (ps + cnt == pend);
         if (seg_end) {
             const int k_hi = kbi + cnt;
@@ -275,7 +312,7 @@ w4a16_stream2_kernel(const StreamArgs a) {
             seg_start = true;
         }
         advance(ps, pend, part, grp, kbi, cnt);
-        buf ^= 1;
+        ++phase;
     }
 
     if (failed && lane == 0) {

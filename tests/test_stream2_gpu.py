@@ -76,11 +76,11 @@ def test_a_wait_that_runs_out_sets_the_status_word_and_returns(hooks, route, var
     layer, g = _layer(n, k, 77 + n)
     image = layer._native_image()
     x = torch.randn(m, k, generator=g).half().cuda()
+    hooks(stream_variant=variant)                                      # the plan (and its scratch) depends on the form
     need = int(lib.b2_w4a16_workspace_bytes(m, n, k))
     ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device="cuda")
     y = torch.zeros(m, n, dtype=torch.float16, device="cuda")
     word = ctypes.c_uint(7)
-    hooks(stream_variant=variant)
     assert _raw_call(lib, x, image, y, ws, n, k, route) == 0
     assert lib.b2_w4a16_status(ws.data_ptr(), None, ctypes.byref(word)) == 0 and word.value == 0
     good = y.clone()
