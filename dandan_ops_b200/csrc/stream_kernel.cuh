@@ -440,9 +440,11 @@ w4a16_stream_kernel(const StreamArgs a) {
                 }
                 if (++stage == kStages) { stage = 0; parity ^= 1u; }
 
-                const float zg = float(zero & 15u), zh = float(zero >> 4);
-                const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);   // even nibbles: (1024+q) - (1024+z)
-                const float eg = -(64.0f + zg), eh = -(64.0f + zh);       // odd nibbles: (1024+16q)/16 - (64+z)
+                // -(1024 + z) for the even nibbles ((1024+q) - (1024+z)) and -(64 + z) for the odd ones
+                // ((1024+16q)/16 - (64+z)) as FP32 bit patterns: z sits in the mantissa, no conversion needed
+                const uint32_t zlo = zero & 15u, zhi = zero >> 4;
+                const float cg = __uint_as_float(0xC4800000u + zlo * 8192u), ch = __uint_as_float(0xC4800000u + zhi * 8192u);
+                const float eg = __uint_as_float(0xC2800000u + zlo * 131072u), eh = __uint_as_float(0xC2800000u + zhi * 131072u);
                 const uint64_t sg = twice(step.x), sh = twice(step.y);
                 const uint8_t* xchunk = xs + ((kb - xorigin) * 4 + t) * kChunk + g * 144;
 #pragma unroll

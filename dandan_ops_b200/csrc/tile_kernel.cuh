@@ -143,9 +143,9 @@ w4a16_tile_kernel(const TileArgs a) {
         const uint4 cb = *reinterpret_cast<const uint4*>(slot + (2 + h) * 512 + lane * 16);   // row g+8
         const float2 step = *reinterpret_cast<const float2*>(slot + kStepOffset + lane * 8);
         const uint32_t zero = slot[kZeroOffset + lane];
-        const float zg = float(zero & 15u), zh = float(zero >> 4);
-        const float cg = -(1024.0f + zg), ch = -(1024.0f + zh);
-        const float eg = -(64.0f + zg), eh = -(64.0f + zh);
+        const uint32_t zlo = zero & 15u, zhi = zero >> 4;      // -(1024 + z), -(64 + z) as FP32 bit patterns
+        const float cg = __uint_as_float(0xC4800000u + zlo * 8192u), ch = __uint_as_float(0xC4800000u + zhi * 8192u);
+        const float eg = __uint_as_float(0xC2800000u + zlo * 131072u), eh = __uint_as_float(0xC2800000u + zhi * 131072u);
         const uint64_t sg = twice(step.x), sh = twice(step.y);
         const uint8_t* xchunk = xs + (b * 4 + t) * kChunk + g * 128;
 #pragma unroll
