@@ -202,6 +202,30 @@ def build_layers(spec, rank, world, device):
     return out
 
 
+def build_fp16_step_layers(spec, device, layers=2):
+    """The same shapes with a state built directly, as the stress configuration builds it: uniform codes and
+    zero points, log-normal steps rounded to FP16 (what checkpoints with FP16 scales hold).  The module then
+    sets B2_FLAG_FP16_STEPS and the kernels run the FP16-only dequantization."""
+    import dandan_ops_b200 as ops
+
+    out = []
+    for li in range(layers):
+        row = []
+        for si, (name, n, k) in enumerate(spec["shapes"]):
+            gen = torch.Generator(device=device)
+            gen.manual_seed(spec["seed"] + 9000 + 100 * li + si)
+            groups = (k + 63) // 64
+            codes = torch.randint(0, 16, (n, k), generator=gen, dtype=torch.uint8, device=device)
+            zero = torch.randint(0, 16, (n, groups), generator=gen, dtype=torch.int32, device=device)
+            step = torch.exp(torch.randn(n, groups, generator=gen, device=device) * 0.5 - 5.0).half().float()
+            layer = ops.QuantizedLinear(ops.pack_int4(codes), step, zero, in_features=k)
+            assert layer._image_flags == 1
+            row.append((name, n, k, layer, n))
+            del codes
+        out.append(row)
+    return out
+
+
 def make_inputs(spec, device, pinned=False):
     xs = {}
     gen = torch.Generator().manual_seed(spec["seed"] + 5)
@@ -455,6 +479,12 @@ def run_gpu(args, rank, world, local_rank):
                 del olayers
                 torch.cuda.empty_cache()
             warm_table = warm_protocol(stream, device)
+            fspec = dict(spec)
+            flayers = build_fp16_step_layers(fspec, device)
+            detail[args.workload + " with FP16-representable steps (B2_FLAG_FP16_STEPS)"] = per_shape_detail(
+                fspec, flayers, make_inputs(fspec, device), stream, device)
+            del flayers
+            torch.cuda.empty_cache()
     cpu = cpu_baseline(spec, sample_seconds=args.cpu_seconds) if (rank == 0 and world == 1 and not args.no_cpu) else None
 
     if rank == 0:

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "b2_w4a16_linear_static": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "b2_w4a16_linear_route": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_linear_bias": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
+    "b2_w4a16_linear_flags": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int, _int]),
     "b2_w4a16_linear_silu_mul": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "b2_w4a16_silu_mul_is_fused": (_int, [_i64, _i64, _i64]),
     "b2_w4a16_silu_mul_pairs": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
@@ -294,14 +295,18 @@ def linear_static(x, image, n, k, out):
     return out
 
 
-def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
-    """y[M,N] = x[M,K] @ W^T (+ FP16 bias [N]) on the current stream.  x must be CUDA FP16 with unit inner stride."""
+FLAG_FP16_STEPS = 1
+
+
+def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None, flags=0):
+    """y[M,N] = x[M,K] @ W^T (+ FP16 bias [N]) on the current stream.  x must be CUDA FP16 with unit inner stride.
+    `flags`: layer flags of the C ABI (FLAG_FP16_STEPS: every step of the layer is FP16-representable)."""
     lib = _lib if _lib is not None else load()
     m = x.shape[0]
     device = x.device
     if torch.cuda.current_device() != device.index:      # rare: keep the common path free of context switches
         with torch.cuda.device(device):
-            return linear(x, image, n, k, route, out, bias)
+            return linear(x, image, n, k, route, out, bias, flags)
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=device)
     if m == 0:
         return y
@@ -313,9 +318,9 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None):
     ws = None if _private else _workspaces.get((device.index, stream))
     if ws is None or ws.numel() < need:
         ws = workspace(device, need)
-    rc = lib.b2_w4a16_linear_bias(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
-                                  bias.data_ptr() if bias is not None else None, y.data_ptr(),
-                                  y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream, route)
+    rc = lib.b2_w4a16_linear_flags(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
+                                   bias.data_ptr() if bias is not None else None, y.data_ptr(),
+                                   y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream, route, flags)
     if rc != OK:
         _check(rc)
     return y

@@ -127,9 +127,9 @@ StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     return p;
 }
 
-template <int MT, bool XVEC, int W>
+template <int MT, bool XVEC, int W, bool H16 = false>
 int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
-    auto kernel = b2::w4a16_stream_kernel<MT, XVEC, W>;
+    auto kernel = b2::w4a16_stream_kernel<MT, XVEC, W, H16>;
     constexpr int smem = b2::stream_smem_bytes(W);
     // Opt in to >48 KB of dynamic shared memory once per device and instantiation.
     static std::atomic<uint64_t> configured{0};
@@ -163,8 +163,11 @@ int launch_stream2_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
 }
 
 template <int MT>
-int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaStream_t s) {
+int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaStream_t s, bool h16) {
     if constexpr (MT <= 2) {
+        // FP16-step chain: up to 16 rows of an aligned x (the decode case it was built for)
+        if (h16 && xvec && warps == 16) return launch_stream_one<MT, true, 16, true>(a, grid, s);
+        if (h16 && xvec && warps == 4) return launch_stream_one<MT, true, 4, true>(a, grid, s);
         if (warps == 32) return xvec ? launch_stream2_one<MT, true, 32>(a, grid, s) : launch_stream2_one<MT, false, 32>(a, grid, s);
         if (warps == 16 && g_stream_variant.load(std::memory_order_relaxed) == 3)
             return xvec ? launch_stream2_one<MT, true, 16>(a, grid, s) : launch_stream2_one<MT, false, 16>(a, grid, s);
@@ -209,9 +212,9 @@ bool tile_applicable(int64_t rows, const b2::Dims& d, int split) {
 
 bool pair_available();
 
-template <int MT, bool XVEC, bool FULL>
+template <int MT, bool XVEC, bool FULL, bool H16 = false>
 int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
-    auto kernel = b2::w4a16_tile_kernel<MT, XVEC, FULL>;
+    auto kernel = b2::w4a16_tile_kernel<MT, XVEC, FULL, H16>;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -242,7 +245,8 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 }
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
-             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0, int sms = 148) {
+             const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0, int sms = 148,
+             bool h16 = false) {
     b2::TileArgs a;
     a.act = act;
     a.x = static_cast<const __half*>(x);
@@ -262,6 +266,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.warps = kb_cta * 2 < b2::kTileMaxWarps ? kb_cta * 2 : b2::kTileMaxWarps;
     if (a.ksplit > 1) {
         const int smem2 = b2::tile_smem_bytes(kb_cta, mt * 8, a.warps) + a.ksplit * mt * 512;      // padded rows: the grid is small
+        if (h16 && xvec) return mt == 1 ? launch_tile_one<1, true, true, true>(a, smem2, s) : launch_tile_one<2, true, true, true>(a, smem2, s);
         if (mt == 1) return xvec ? launch_tile_one<1, true, true>(a, smem2, s) : launch_tile_one<1, false, true>(a, smem2, s);
         return xvec ? launch_tile_one<2, true, true>(a, smem2, s) : launch_tile_one<2, false, true>(a, smem2, s);
     }
@@ -271,6 +276,10 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     const int per_sm = padded <= kTileSmemLimit ? std::min(227 * 1024 / (padded + 1024), 2048 / (a.warps * 32)) : 0;
     const bool full = rows == mt * 8 || int64_t(d.n16) <= int64_t(per_sm) * (sms > 0 ? sms : 148);
     const int smem = b2::tile_smem_bytes(d.kb, full ? mt * 8 : int(rows), a.warps);
+    if (h16 && xvec) {
+        if (mt == 1) return full ? launch_tile_one<1, true, true, true>(a, smem, s) : launch_tile_one<1, true, false, true>(a, smem, s);
+        return full ? launch_tile_one<2, true, true, true>(a, smem, s) : launch_tile_one<2, true, false, true>(a, smem, s);
+    }
     if (mt == 1) {
         if (full) return xvec ? launch_tile_one<1, true, true>(a, smem, s) : launch_tile_one<1, false, true>(a, smem, s);
         return xvec ? launch_tile_one<1, true, false>(a, smem, s) : launch_tile_one<1, false, false>(a, smem, s);
@@ -281,7 +290,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
                const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s,
-               const DeviceInfo& dev, const void* bias, int act = 0) {
+               const DeviceInfo& dev, const void* bias, int act = 0, bool h16 = false) {
     const int64_t ticket_bytes = B2_W4A16_TICKET_BYTES;
     const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
     for (int64_t m0 = 0; m0 < m; m0 += B2_STREAM_MAX_M) {
@@ -306,10 +315,10 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.fault_step = g_fault_step.exchange(-1, std::memory_order_relaxed);
         int rc;
         switch (p.mt) {
-            case 1: rc = launch_stream<1>(a, xvec, p.warps, p.grid, s); break;
-            case 2: rc = launch_stream<2>(a, xvec, p.warps, p.grid, s); break;
-            case 4: rc = launch_stream<4>(a, xvec, p.warps, p.grid, s); break;
-            default: rc = launch_stream<8>(a, xvec, p.warps, p.grid, s); break;
+            case 1: rc = launch_stream<1>(a, xvec, p.warps, p.grid, s, h16); break;
+            case 2: rc = launch_stream<2>(a, xvec, p.warps, p.grid, s, h16); break;
+            case 4: rc = launch_stream<4>(a, xvec, p.warps, p.grid, s, h16); break;
+            default: rc = launch_stream<8>(a, xvec, p.warps, p.grid, s, h16); break;
         }
         if (rc != B2_OK) return rc;
     }
@@ -399,9 +408,9 @@ int launch_gemm_one(const CUtensorMap& map, const b2::GemmArgs& a, dim3 grid, cu
     return after_launch("w4a16_gemm_kernel");
 }
 
-template <int MT, bool TMA_Y>
+template <int MT, bool TMA_Y, bool H16 = false>
 int launch_gemm_pair(const CUtensorMap& map, const CUtensorMap& ymap, const b2::GemmArgs& a, dim3 grid, cudaStream_t s) {
-    auto kernel = b2::w4a16_gemm_pair_kernel<MT, TMA_Y>;
+    auto kernel = b2::w4a16_gemm_pair_kernel<MT, TMA_Y, H16>;
     constexpr int smem = b2::pair_smem_bytes<MT>();
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -523,7 +532,7 @@ GemmShape gemm_shape_for_call(int64_t m, const b2::Dims& d, int sms, int64_t wor
 
 int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
              const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s, int sms, const void* bias,
-             int act = 0) {
+             int act = 0, bool h16 = false) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return fail(B2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from the driver");
     if (workspace == nullptr) return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
@@ -564,6 +573,7 @@ int run_gemm(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
             if (encode(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, y, ydims, ystrides, ybox, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
                 return fail(B2_ERR_CUDA, "cuTensorMapEncodeTiled failed for y");
+            if (h16) return pair_mt == 256 ? launch_gemm_pair<256, true, true>(map, ymap, a, pgrid, s) : launch_gemm_pair<192, true, true>(map, ymap, a, pgrid, s);
             return pair_mt == 256 ? launch_gemm_pair<256, true>(map, ymap, a, pgrid, s) : launch_gemm_pair<192, true>(map, ymap, a, pgrid, s);
         }
         return pair_mt == 256 ? launch_gemm_pair<256, false>(map, ymap, a, pgrid, s) : launch_gemm_pair<192, false>(map, ymap, a, pgrid, s);
@@ -806,7 +816,8 @@ residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, i
 // act = 1: rows g / g+8 of every 16-row tile are a gate/up pair and y gets n/2 columns.
 int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                 int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
-                int64_t workspace_bytes, void* stream, int route, int act) {
+                int64_t workspace_bytes, void* stream, int route, int act, int flags = 0) {
+    const bool h16 = (flags & B2_FLAG_FP16_STEPS) != 0;
     const void* bias = bias_fp16;
     if (bias && reinterpret_cast<uintptr_t>(bias) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
     if (m < 0) return fail(B2_ERR_ARGUMENT, "m must be non-negative");
@@ -840,17 +851,17 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
         if (!tile_applicable(m, d, tile_split))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
-        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count);
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count, h16);
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
-                          static_cast<cudaStream_t>(stream), dev, bias, act);
+                          static_cast<cudaStream_t>(stream), dev, bias, act, h16);
     if (route == B2_ROUTE_TCGEN05) {
         if (!gemm_applicable(x, ldx, d))
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
         if (workspace_bytes < B2_W4A16_TICKET_BYTES)
             return fail(B2_ERR_WORKSPACE, "workspace smaller than b2_w4a16_workspace_bytes()");
-        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), dev.sm_count, bias, act);
+        return run_gemm(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), dev.sm_count, bias, act, h16);
     }
     return fail(B2_ERR_UNSUPPORTED, "unknown route");
 }
@@ -863,6 +874,13 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
                          int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                          int64_t workspace_bytes, void* stream, int route) {
     return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, route, 0);
+}
+
+int b2_w4a16_linear_flags(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                          int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                          int64_t workspace_bytes, void* stream, int route, int flags) {
+    if (flags & ~B2_FLAG_FP16_STEPS) return fail(B2_ERR_ARGUMENT, "unknown flag");
+    return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, route, 0, flags);
 }
 
 int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,

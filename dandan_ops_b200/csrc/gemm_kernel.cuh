@@ -120,6 +120,12 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 
 // Eight weights of one native word -> eight FP16 values in column order (16 bytes).
 // s2 = twice(step), c_even = -(1024 + zero), c_odd = -(64 + zero).
+template <bool H16>
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, const GroupConst<H16>& g) {
+    const uint32_t u = w >> 8;
+    return make_uint4(dq_even<H16>(and_or(w, 0x000F000Fu, 0x64006400u), g), dq_odd<H16>(and_or(w, 0x00F000F0u, 0x64006400u), g),
+                      dq_even<H16>(and_or(u, 0x000F000Fu, 0x64006400u), g), dq_odd<H16>(and_or(u, 0x00F000F0u, 0x64006400u), g));
+}
 __device__ __forceinline__ uint4 dequant_word(uint32_t w, float c_even, float c_odd, uint64_t s2) {
     const uint32_t u = w >> 8;
     return make_uint4(dequant_pair_even(and_or(w, 0x000F000Fu, 0x64006400u), c_even, s2),

@@ -134,7 +134,7 @@ __device__ __forceinline__ void tma_store_wait_read() {
 // TMA_Y: y is 16-byte aligned with a row stride that is a multiple of 16 bytes; the epilogue
 // then transposes through shared memory (the idle x ring) and stores each warp's 32 columns x
 // MT/2 rows with one TMA store.  Otherwise every thread stores its 2-byte results itself.
-template <int MT, bool TMA_Y>
+template <int MT, bool TMA_Y, bool H16 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, PairShape<MT>::CTAS)
 w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap ymap, const GemmArgs a) {
     constexpr int XS = PairShape<MT>::XS, WS = PairShape<MT>::WS, RS = PairShape<MT>::RS;
@@ -274,14 +274,12 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_co
             const uint4 code0 = *reinterpret_cast<const uint4*>(nb + (2 * hi8) * 512 + lane_idx * 16);
             const uint4 code1 = *reinterpret_cast<const uint4*>(nb + (2 * hi8 + 1) * 512 + lane_idx * 16);
             const float step = *reinterpret_cast<const float*>(nb + kStepOffset + (lane_idx * 2 + hi8) * 4);
-            const float z = float((nb[kZeroOffset + lane_idx] >> (4 * hi8)) & 15);
-            const float c_even = -(1024.0f + z), c_odd = -(64.0f + z);
-            const uint64_t step2 = twice(step);
+            const GroupConst<H16> gc = make_group<H16>((nb[kZeroOffset + lane_idx] >> (4 * hi8)) & 15u, step);
             const uint32_t words[8] = {code0.x, code0.y, code0.z, code0.w, code1.x, code1.y, code1.z, code1.w};
             uint32_t o[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint4 q = dequant_word(words[i], c_even, c_odd, step2);
+                const uint4 q = dequant_word<H16>(words[i], gc);
                 o[4 * i] = q.x; o[4 * i + 1] = q.y; o[4 * i + 2] = q.z; o[4 * i + 3] = q.w;
             }
             // the conversion happens in registers before the wait for the free tensor-memory stage

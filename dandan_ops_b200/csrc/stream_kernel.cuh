@@ -246,6 +246,58 @@ __device__ __forceinline__ uint32_t dequant_pair_odd(uint32_t h2, float c, uint6
     return *reinterpret_cast<uint32_t*>(&p);
 #endif
 }
+// ---- the two dequantization chains behind one interface -------------------------------------
+// Exact<false>: the general chain above (FP32 step, FP32 multiply, one cvt per pair).
+// Exact<true> ("FP16 steps"): for layers whose steps are all exactly representable in FP16 - checkpoints
+// that store FP16 scales - the product (code - zero) * step has at most 15 significant bits, so it is exact
+// in FP32 and fp16_rn(fp32(code - zero) * step) == hmul2(code - zero, step): one FP16 subtract (or fma by
+// 1/16 for the odd nibbles) and one FP16 multiply per pair, bit-identical to the general chain.
+template <bool H16> struct GroupConst;
+template <> struct GroupConst<false> {
+    float c_even, c_odd;     // -(1024 + z), -(64 + z)
+    uint64_t s2;             // the step, twice
+};
+template <> struct GroupConst<true> {
+    uint32_t z_even, z_odd;  // FP16 pairs (1024 + z), -(64 + z)
+    uint32_t s2;             // FP16 pair (step, step)
+};
+template <bool H16>
+__device__ __forceinline__ GroupConst<H16> make_group(uint32_t z, float step) {
+    GroupConst<H16> g;
+    if constexpr (H16) {
+        g.z_even = 0x64006400u + z * 0x00010001u;          // 1024 has ulp 1: z sits in the mantissa
+        g.z_odd = 0xD400D400u + z * 0x00100010u;           // -(64 + z): 64 has ulp 1/16
+        asm("cvt.rn.f16x2.f32 %0, %1, %1;" : "=r"(g.s2) : "f"(step));
+    } else {
+        // -(1024 + z) and -(64 + z) as FP32 bit patterns: z sits in the mantissa, no int-to-float conversion
+        g.c_even = __uint_as_float(0xC4800000u + z * 8192u);
+        g.c_odd = __uint_as_float(0xC2800000u + z * 131072u);
+        g.s2 = twice(step);
+    }
+    return g;
+}
+template <bool H16>
+__device__ __forceinline__ uint32_t dq_even(uint32_t h2, const GroupConst<H16>& g) {      // h2 = (1024 + code) pair
+    if constexpr (H16) {
+        uint32_t r;
+        asm("{\n\t.reg .b32 d;\n\tsub.rn.f16x2 d, %1, %2;\n\tmul.rn.f16x2 %0, d, %3;\n\t}"
+            : "=r"(r) : "r"(h2), "r"(g.z_even), "r"(g.s2));
+        return r;
+    } else {
+        return dequant_pair_even(h2, g.c_even, g.s2);
+    }
+}
+template <bool H16>
+__device__ __forceinline__ uint32_t dq_odd(uint32_t h2, const GroupConst<H16>& g) {       // h2 = (1024 + 16 * code) pair
+    if constexpr (H16) {
+        uint32_t r;
+        asm("{\n\t.reg .b32 d, q;\n\tmov.b32 q, 0x2C002C00;\n\tfma.rn.f16x2 d, %1, q, %2;\n\tmul.rn.f16x2 %0, d, %3;\n\t}"
+            : "=r"(r) : "r"(h2), "r"(g.z_odd), "r"(g.s2));
+        return r;
+    } else {
+        return dequant_pair_odd(h2, g.c_odd, g.s2);
+    }
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -326,7 +378,7 @@ __device__ __forceinline__ int owner_of(int s, int steps, int ctas) {
 
 // MT = number of 8-row tiles of x (1, 2, 4 or 8).  XVEC: x rows are 16-byte aligned and
 // K is a multiple of 8, so x is read with 16-byte loads.
-template <int MT, bool XVEC, int W>
+template <int MT, bool XVEC, int W, bool H16 = false>
 __global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
 w4a16_stream_kernel(const StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -440,12 +492,7 @@ w4a16_stream_kernel(const StreamArgs a) {
                 }
                 if (++stage == kStages) { stage = 0; parity ^= 1u; }
 
-                // -(1024 + z) for the even nibbles ((1024+q) - (1024+z)) and -(64 + z) for the odd ones
-                // ((1024+16q)/16 - (64+z)) as FP32 bit patterns: z sits in the mantissa, no conversion needed
-                const uint32_t zlo = zero & 15u, zhi = zero >> 4;
-                const float cg = __uint_as_float(0xC4800000u + zlo * 8192u), ch = __uint_as_float(0xC4800000u + zhi * 8192u);
-                const float eg = __uint_as_float(0xC2800000u + zlo * 131072u), eh = __uint_as_float(0xC2800000u + zhi * 131072u);
-                const uint64_t sg = twice(step.x), sh = twice(step.y);
+                const GroupConst<H16> gg = make_group<H16>(zero & 15u, step.x), gh = make_group<H16>(zero >> 4, step.y);
                 const uint8_t* xchunk = xs + ((kb - xorigin) * 4 + t) * kChunk + g * 144;
 #pragma unroll
                 for (int wi = 0; wi < 8; ++wi) {
@@ -458,10 +505,10 @@ w4a16_stream_kernel(const StreamArgs a) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
-                        const uint32_t w[4] = {dequant_pair_even(and_or(ua, 0x000F000Fu, 0x64006400u), cg, sg),
-                                               dequant_pair_even(and_or(ub, 0x000F000Fu, 0x64006400u), ch, sh),
-                                               dequant_pair_odd(and_or(ua, 0x00F000F0u, 0x64006400u), eg, sg),
-                                               dequant_pair_odd(and_or(ub, 0x00F000F0u, 0x64006400u), eh, sh)};
+                        const uint32_t w[4] = {dq_even<H16>(and_or(ua, 0x000F000Fu, 0x64006400u), gg),
+                                               dq_even<H16>(and_or(ub, 0x000F000Fu, 0x64006400u), gh),
+                                               dq_odd<H16>(and_or(ua, 0x00F000F0u, 0x64006400u), gg),
+                                               dq_odd<H16>(and_or(ub, 0x00F000F0u, 0x64006400u), gh)};
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt)
                             mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);

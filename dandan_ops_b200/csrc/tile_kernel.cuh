@@ -58,7 +58,7 @@ __host__ __device__ constexpr int tile_smem_bytes(int kb, int rows, int warps) {
 // FULL: all MT * 8 rows of x are staged (zeros beyond M): compile-time layout, no row predicates -
 // the faster form whenever the padded rows do not cost occupancy.  Otherwise only the M rows that
 // exist are staged and lanes of missing rows use zero fragments.
-template <int MT, bool XVEC, bool FULL>
+template <int MT, bool XVEC, bool FULL, bool H16 = false>
 __global__ void __launch_bounds__(kTileMaxWarps * 32)
 w4a16_tile_kernel(const TileArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -143,10 +143,7 @@ w4a16_tile_kernel(const TileArgs a) {
         const uint4 cb = *reinterpret_cast<const uint4*>(slot + (2 + h) * 512 + lane * 16);   // row g+8
         const float2 step = *reinterpret_cast<const float2*>(slot + kStepOffset + lane * 8);
         const uint32_t zero = slot[kZeroOffset + lane];
-        const uint32_t zlo = zero & 15u, zhi = zero >> 4;      // -(1024 + z), -(64 + z) as FP32 bit patterns
-        const float cg = __uint_as_float(0xC4800000u + zlo * 8192u), ch = __uint_as_float(0xC4800000u + zhi * 8192u);
-        const float eg = __uint_as_float(0xC2800000u + zlo * 131072u), eh = __uint_as_float(0xC2800000u + zhi * 131072u);
-        const uint64_t sg = twice(step.x), sh = twice(step.y);
+        const GroupConst<H16> gg = make_group<H16>(zero & 15u, step.x), gh = make_group<H16>(zero >> 4, step.y);
         const uint8_t* xchunk = xs + (b * 4 + t) * kChunk + g * 128;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -159,10 +156,10 @@ w4a16_tile_kernel(const TileArgs a) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const uint32_t ua = wa >> (8 * e), ub = wb >> (8 * e);
-const uint32_t w[4] = {dequant_pair_even(and_or(ua, 0x000F000Fu, 0x64006400u), cg, sg),
-                                       dequant_pair_even(and_or(ub, 0x000F000Fu, 0x64006400u), ch, sh),
-                                       dequant_pair_odd(and_or(ua, 0x00F000F0u, 0x64006400u), eg, sg),
-                                       dequant_pair_odd(and_or(ub, 0x00F000F0u, 0x64006400u), eh, sh)};
+                const uint32_t w[4] = {dq_even<H16>(and_or(ua, 0x000F000Fu, 0x64006400u), gg),
+                                       dq_even<H16>(and_or(ub, 0x000F000Fu, 0x64006400u), gh),
+                                       dq_odd<H16>(and_or(ua, 0x00F000F0u, 0x64006400u), gg),
+                                       dq_odd<H16>(and_or(ub, 0x00F000F0u, 0x64006400u), gh)};
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
                     mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);

@@ -115,7 +115,7 @@ void check_w4a16(const at::Tensor& x, const at::Tensor& packed, const at::Tensor
 }
 
 at::Tensor run_image(const at::Tensor& x, const at::Tensor& image, int64_t n, int64_t k, const c10::optional<at::Tensor>& bias,
-                     int64_t route) {
+                     int64_t route, int64_t flags = 0) {
     c10::cuda::CUDAGuard guard(x.device());
     const int64_t m = x.size(0);
     at::Tensor y = at::empty({m, n}, x.options());
@@ -123,8 +123,8 @@ at::Tensor run_image(const at::Tensor& x, const at::Tensor& image, int64_t n, in
     cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
     at::Tensor ws = workspace_for(x.device(), stream, b2_w4a16_workspace_bytes(m, n, k));
     const void* bias_ptr = bias.has_value() && bias->defined() ? bias->data_ptr() : nullptr;
-    check_rc(b2_w4a16_linear_bias(x.data_ptr(), m > 1 ? x.stride(0) : k, image.data_ptr(), bias_ptr, y.data_ptr(), n, m, n, k,
-                                  ws.data_ptr(), ws.numel(), stream, int(route)));
+    check_rc(b2_w4a16_linear_flags(x.data_ptr(), m > 1 ? x.stride(0) : k, image.data_ptr(), bias_ptr, y.data_ptr(), n, m, n, k,
+                                   ws.data_ptr(), ws.numel(), stream, int(route), int(flags)));
     return y;
 }
 
@@ -142,9 +142,10 @@ at::Tensor legacy_op(const at::Tensor& x, const at::Tensor& packed, const at::Te
     return run_image(x, image_for(packed, scales, zeros, x.size(1)), packed.size(0), x.size(1), c10::nullopt, B2_ROUTE_AUTO);
 }
 
-// x [M, K] FP16 with unit inner stride, image = device-native weight image, bias = FP16 [N] or None.
+// x [M, K] FP16 with unit inner stride, image = device-native weight image, bias = FP16 [N] or None,
+// flags = layer flags of the C ABI (B2_FLAG_FP16_STEPS).
 at::Tensor linear_image(const at::Tensor& x, const at::Tensor& image, int64_t n, int64_t k, const c10::optional<at::Tensor>& bias,
-                        int64_t route) {
+                        int64_t route, int64_t flags) {
     TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kHalf && x.dim() == 2 && x.size(1) == k && x.stride(1) == 1 &&
                     (x.size(0) <= 1 || x.stride(0) >= k), "x must be a CUDA FP16 [M, K] tensor with unit inner stride");
     TORCH_CHECK(image.is_cuda() && image.scalar_type() == at::kByte && image.device() == x.device() &&
@@ -152,7 +153,7 @@ at::Tensor linear_image(const at::Tensor& x, const at::Tensor& image, int64_t n,
     if (bias.has_value() && bias->defined())
         TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kHalf && bias->numel() == n && bias->is_contiguous(),
                     "bias must be a contiguous CUDA FP16 [N] tensor");
-    return run_image(x, image, n, k, bias, route);
+    return run_image(x, image, n, k, bias, route, flags);
 }
 
 int64_t status_all() {
@@ -180,7 +181,7 @@ TORCH_LIBRARY_FRAGMENT(dandan_ops, m) {
     m.def("w4a16_gemv(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size) -> Tensor");
     m.def("w4a16_tensorcore(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size) -> Tensor");
     m.def("w4a16_small(Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size) -> Tensor");
-    m.def("w4a16_linear_image(Tensor x, Tensor image, int n, int k, Tensor? bias, int route) -> Tensor");
+    m.def("w4a16_linear_image(Tensor x, Tensor image, int n, int k, Tensor? bias, int route, int flags) -> Tensor");
     m.def("w4a16_workspace_status() -> int", &status_all);
 }
 

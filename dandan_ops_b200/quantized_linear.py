@@ -82,14 +82,14 @@ def _image_for(packed, scales, zeros, in_features):
     return image
 
 
-def _engine(x, image, rows, in_features, bias16):
-    """`bias16`: the bias already converted to FP16 (or None).  The kernels round the product to
+def _engine(x, image, rows, in_features, bias16, flags=0):
+    """`bias16`: the bias already converted to FP16 (or None); `flags`: layer flags of the C ABI.  The kernels round the product to
     FP16 first and add the FP16 bias afterwards, as the reference's `y + bias.to(y.dtype)` does."""
     if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < in_features):
         x = x.contiguous()
     if _ops_module.SHIM_LOADED:       # C++ operator library: output, workspace and launch without a ctypes round trip
-        return torch.ops.dandan_ops.w4a16_linear_image(x, image, rows, in_features, bias16, 0)
-    return _native.linear(x, image, rows, in_features, bias=bias16)
+        return torch.ops.dandan_ops.w4a16_linear_image(x, image, rows, in_features, bias16, 0, flags)
+    return _native.linear(x, image, rows, in_features, bias=bias16, flags=flags)
 
 
 def quantized_linear(x, packed_weight, scales, zeros, *, in_features, group_size=64, bias=None,
@@ -137,6 +137,7 @@ class QuantizedLinear(torch.nn.Module):
         self.register_buffer("bias", None if bias is None else bias.detach().clone().contiguous())
         self._image = None
         self._image_key = None
+        self._image_flags = 0
         self._bias16 = None
         self._bias16_key = None
         self._checked_key = None
@@ -220,7 +221,17 @@ class QuantizedLinear(torch.nn.Module):
         if self._image is None or self._image_key != key:
             self._image = _native.repack(self.packed_weight, self.scales, self.zeros, self.in_features)
             self._image_key = key
+            self._image_flags = self._layer_flags()
         return self._image
+
+    def _layer_flags(self):
+        """Flags of the C ABI for this state.  FLAG_FP16_STEPS when every step is exactly representable in
+        FP16 (checkpoints with FP16 scales): the decode kernels then use the FP16-only dequantization, which
+        is bit-identical for such steps.  Reads the steps once (a host sync), only when an image is (re)built -
+        never on the per-token path - and not while a stream is being captured."""
+        if not self.scales.is_cuda or torch.cuda.is_current_stream_capturing():
+            return 0
+        return _native.FLAG_FP16_STEPS if bool((self.scales.half().float() == self.scales).all()) else 0
 
     def attach_native_image(self, image):
         """Use a prebuilt device image of THIS layer's state (e.g. from `checkpoint.ImageCache`)
@@ -231,6 +242,7 @@ class QuantizedLinear(torch.nn.Module):
         self._image = image
         self._image_key = (self.packed_weight.data_ptr(), self.scales.data_ptr(), self.zeros.data_ptr(),
                            self.packed_weight._version, self.scales._version, self.zeros._version)
+        self._image_flags = self._layer_flags()
 
     def _bias_fp16(self):
         """FP16 copy of the bias for the fused epilogue (derived, rebuilt when the bias changes)."""
@@ -293,7 +305,7 @@ class QuantizedLinear(torch.nn.Module):
         if (key == self._checked_key and type(x) is torch.Tensor and x.dtype is torch.float16 and x.ndim == 2
                 and x.shape[1] == self.in_features and x.device == self._checked_device
                 and not (x.requires_grad and torch.is_grad_enabled())):
-            return _engine(x, self._image, self.out_features, self.in_features, self._bias_fp16())
+            return _engine(x, self._image, self.out_features, self.in_features, self._bias_fp16(), self._image_flags)
         y = self._forward_checked(x)
         if self.backend in ("auto", "cuda", "tensorcore", "naive") and not self.scales.requires_grad \
                 and self._image is not None:
@@ -312,7 +324,9 @@ class QuantizedLinear(torch.nn.Module):
         _resolve(x, self.scales, self.group_size, self.backend)
         if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < self.in_features):
             x = x.contiguous()
-        return _native.linear(x, self._native_image(), self.out_features, self.in_features, out=out, bias=self._bias_fp16())
+        image = self._native_image()
+        return _native.linear(x, image, self.out_features, self.in_features, out=out, bias=self._bias_fp16(),
+                              flags=self._image_flags)
 
     def _forward_checked(self, x):
         validate_int4_state(self.packed_weight, self.scales, self.zeros, self.in_features, self.group_size)
@@ -324,4 +338,5 @@ class QuantizedLinear(torch.nn.Module):
             raise ValueError("x and quantized weight must share a device")
         _check_bias(self.bias, self.out_features, x.device)
         _resolve(x, self.scales, self.group_size, self.backend)
-        return _engine(x, self._native_image(), self.out_features, self.in_features, self._bias_fp16())
+        image = self._native_image()
+        return _engine(x, image, self.out_features, self.in_features, self._bias_fp16(), self._image_flags)

@@ -158,6 +158,18 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
                          int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                          int64_t workspace_bytes, void* stream, int route);
 
+/* Same with layer flags.  B2_FLAG_FP16_STEPS: the caller asserts that EVERY step (scale) of the layer is
+ * exactly representable in FP16 - true for checkpoints that store FP16 scales.  The decode kernels (M <= 16,
+ * 16-byte aligned x) and the converters of the pair GEMM (16-byte aligned y) then dequantize with two FP16 instructions per weight pair instead of the mixed-precision
+ * chain: (code - zero) * step has at most 15 significant bits, so fp16_rn(fp32(code - zero) * step) ==
+ * hmul2(code - zero, step) and the weights are bit-identical to the general path.  The flag changes speed only;
+ * set on a layer with other steps it gives wrong weights.  No counterpart in the reference (its kernels
+ * multiply in FP32 throughout, kernels/w4a16_small.cuh:39). */
+#define B2_FLAG_FP16_STEPS 1
+int b2_w4a16_linear_flags(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                          int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                          int64_t workspace_bytes, void* stream, int route, int flags);
+
 /* Fused gate/up projection of a gated MLP: y[M, N/2] = SiLU(g) * u with g, u = the FP16 outputs
  * (bias included) of the gate and up rows, rounded as the reference's separate launch does
  * (`silu_and_mul`: SiLU rounded to FP16 before the multiplication, dandan_ops/elementwise.py:168-173,
