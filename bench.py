@@ -318,7 +318,7 @@ def run_gpu(args, rank, world, local_rank):
     if gather_on:
         from dandan_ops_b200.sharded import ColumnShardedLinear, PeerArena
         need = sum(2 * (-(-(m * n_full * 2) // 256) * 256) for m in spec["ms"] for row in layers for (_, _, _, _, n_full) in row)
-        arena = PeerArena(need + (1 << 20))
+        arena = PeerArena(need + (1 << 20))      # slices up to 1 MB travel as polled packets (the decode sizes)
     calls = []
     for li, row in enumerate(layers):
         for (name, n, k, layer, n_full) in row:
@@ -378,7 +378,8 @@ def run_gpu(args, rank, world, local_rank):
             for c in calls:
                 sl = c["sharded"]
                 full, ptrs = sl.arena.output((id(sl), 0), c["m"], c["n_full"])
-                _native.gather(ptrs, sl.arena.flag_ptrs, rank, c["m"], c["n_full"], sl.rows[0], sl.rows[1] - sl.rows[0])
+                _native.gather(ptrs, sl.arena.flag_ptrs, sl.arena.mailbox_slice_bytes, rank, c["m"], c["n_full"], c["n_full"],
+                               sl.rows_per_rank)
         gather_graph = capture(gather_step, stream) if gather_on else None
         floor_graph = capture(lambda: [_native.noop() for _ in range(launches_per_step)], stream)
         warm = max(args.warmup, 3)
@@ -538,7 +539,8 @@ def run_gpu(args, rank, world, local_rank):
                               "how": "the same step with one eager Python call per linear"}},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks.summary(),
-            "roofline_prefill": prefill_roofline(detail),
+            "roofline_prefill": prefill_roofline({k: v for k, v in (detail or {}).items() if "FP16" not in k}),
+            "roofline_prefill_fp16_steps": prefill_roofline({k: v for k, v in (detail or {}).items() if "FP16" in k}),
             "warm": warm_table,
             "detail": detail,
         }

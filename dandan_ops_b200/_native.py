@@ -27,7 +27,8 @@ _SIGNATURES = {
     "b2_w4a16_launch_count": (_i64, []),
     "b2_w4a16_set_gemm_shape": (_int, [_int, _int]),
     "b2_w4a16_test_hooks": (_int, [_int, _int, _int]),
-    "b2_w4a16_gather": (_int, [ctypes.POINTER(_vp), ctypes.POINTER(_vp), _int, _int, _i64, _i64, _i64, _i64, _vp]),
+    "b2_w4a16_gather": (_int, [ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _int, _int, _i64, _i64, _i64, _i64, _vp]),
+    "b2_w4a16_gather_block_bytes": (_i64, [_int, _i64]),
     "b2_w4a16_gather_status": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_uint)]),
     "b2_w4a16_gather_wait_limit": (_int, [_i64]),
     "b2_w4a16_noop": (_int, [_vp]),
@@ -112,16 +113,19 @@ def test_hooks(wait_limit=0, skip_copy=-1, stream_variant=0):
     _need_cache.clear()
 
 
-GATHER_FLAG_BYTES = 128
+def gather_block_bytes(world, mailbox_slice_bytes):
+    """Bytes of one rank's flag block + packet mailbox (`b2_w4a16_gather_block_bytes`)."""
+    return int(load().b2_w4a16_gather_block_bytes(world, mailbox_slice_bytes))
 
 
-def gather(y_ptrs, flag_ptrs, rank, m, ld, col0, cols):
+def gather(y_ptrs, flag_ptrs, mailbox_slice_bytes, rank, m, ld, n_total, slice_cols):
     """`b2_w4a16_gather` on the current stream: `y_ptrs` / `flag_ptrs` are per-rank device addresses
-    (ints) of the [m, ld] FP16 buffers and flag blocks as mapped into this process."""
+    (ints) of the [m, ld] FP16 buffers and flag blocks as mapped into this process; rank q owns the
+    columns [q * slice_cols, min(n_total, (q + 1) * slice_cols))."""
     world = len(y_ptrs)
     ys = (_vp * world)(*y_ptrs)
     fs = (_vp * world)(*flag_ptrs)
-    _check(load().b2_w4a16_gather(ys, fs, rank, world, m, ld, col0, cols, _stream()))
+    _check(load().b2_w4a16_gather(ys, fs, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, _stream()))
 
 
 def gather_status(flag_ptr):

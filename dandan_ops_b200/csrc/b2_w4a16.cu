@@ -996,32 +996,52 @@ int b2_w4a16_linear_static(const void* x, int64_t ldx, const void* native, void*
                                  B2_ROUTE_STREAM);
 }
 
-int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int rank, int world, int64_t m, int64_t ld,
-                    int64_t col0, int64_t cols, void* stream) {
+int64_t b2_w4a16_gather_block_bytes(int world, int64_t mailbox_slice_bytes) {
+    if (world < 1 || world > b2::kGatherMaxRanks || mailbox_slice_bytes < 0) return 0;
+    // flag words + [2 parities][world senders][one 8-byte packet per 4-byte word of a slice]
+    return b2::kGatherMailboxOffset + 2 * int64_t(world) * (mailbox_slice_bytes / 4) * 8;
+}
+
+int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world,
+                    int64_t m, int64_t ld, int64_t n_total, int64_t slice_cols, void* stream) {
     if (!y_ranks || !flag_blocks) return fail(B2_ERR_ARGUMENT, "null pointer");
     if (world < 1 || world > b2::kGatherMaxRanks || rank < 0 || rank >= world)
         return fail(B2_ERR_ARGUMENT, "rank / world out of range (at most 16 ranks)");
-    if (m < 0 || cols < 0 || col0 < 0 || ld < col0 + cols) return fail(B2_ERR_ARGUMENT, "slice outside the row");
+    if (m < 0 || n_total < 0 || slice_cols <= 0 || ld < n_total || slice_cols * world < n_total || mailbox_slice_bytes < 0)
+        return fail(B2_ERR_ARGUMENT, "slices do not cover the row");
     if (m > INT_MAX) return fail(B2_ERR_RANGE, "m exceeds the kernel index range");
+    const int64_t col0 = std::min(n_total, int64_t(rank) * slice_cols);
+    const int64_t cols = std::min(slice_cols, n_total - col0);
     b2::GatherArgs a;
     bool vec = col0 % 8 == 0 && cols % 8 == 0 && ld % 8 == 0;
+    bool words = slice_cols % 2 == 0 && n_total % 2 == 0 && ld % 2 == 0;
     for (int q = 0; q < b2::kGatherMaxRanks; ++q) {
         a.y[q] = q < world ? static_cast<__half*>(y_ranks[q]) : nullptr;
         a.flags[q] = q < world ? static_cast<unsigned*>(flag_blocks[q]) : nullptr;
         if (q < world) {
-            if (!a.flags[q] || (!a.y[q] && m * cols > 0)) return fail(B2_ERR_ARGUMENT, "null pointer");
-            if (reinterpret_cast<uintptr_t>(a.flags[q]) % 4 || reinterpret_cast<uintptr_t>(a.y[q]) % 2)
+            if (!a.flags[q] || (!a.y[q] && m * n_total > 0)) return fail(B2_ERR_ARGUMENT, "null pointer");
+            if (reinterpret_cast<uintptr_t>(a.flags[q]) % 8 || reinterpret_cast<uintptr_t>(a.y[q]) % 2)
                 return fail(B2_ERR_ARGUMENT, "misaligned buffer");
             vec = vec && reinterpret_cast<uintptr_t>(a.y[q]) % 16 == 0;
+            words = words && reinterpret_cast<uintptr_t>(a.y[q]) % 4 == 0;
         }
     }
     a.rank = rank; a.world = world; a.m = int(m); a.ld = ld; a.col0 = col0; a.cols = cols;
+    a.n_total = n_total; a.slice_cols = slice_cols; a.slots = mailbox_slice_bytes / 4;
     a.wait_ns = g_gather_wait_ns.load(std::memory_order_relaxed);
     DeviceInfo dev;
     if (int rc = device_info(dev)) return rc;
+    const int sms = dev.sm_count > 0 ? dev.sm_count : 148;
+    // Small slices (every rank's fits in a mailbox half): packets polled by the receiver, one NVLink crossing.
+    if (words && world > 1 && m * slice_cols * 2 <= mailbox_slice_bytes && m * slice_cols > 0) {
+        const int64_t items = m * (slice_cols / 2) * (world - 1);
+        const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>((items + 255) / 256, 2LL * sms)));
+        b2::gather_mailbox_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+        return after_launch("gather_mailbox_kernel");
+    }
     const int64_t items = m * (vec ? cols / 8 : cols) * (world - 1);
     const int64_t want = (items + 255) / 256;
-    const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(want, 2LL * (dev.sm_count > 0 ? dev.sm_count : 148))));
+    const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(want, 2LL * sms)));
     if (vec) b2::gather_push_wait_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
     else b2::gather_push_wait_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return after_launch("gather_push_wait_kernel");

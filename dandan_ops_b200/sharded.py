@@ -48,7 +48,10 @@ class PeerArena:
 
     ALIGN = 256
 
-    def __init__(self, nbytes, group=None, device=None):
+    def __init__(self, nbytes, group=None, device=None, mailbox_slice_bytes=1 << 20):
+        """`nbytes`: room for the gathered outputs.  `mailbox_slice_bytes`: largest slice (bytes of one
+        rank's columns of one output) that travels as polled packets instead of push + flags (costs
+        4 * world * mailbox_slice_bytes of the arena; 0 = never)."""
         import torch.distributed._symmetric_memory as symm
 
         group = dist.group.WORLD if group is None else group
@@ -61,7 +64,10 @@ class PeerArena:
                 pass
             symm.enable_symm_mem_for_group(group.group_name)
         self.group = group
-        self.bytes = int(nbytes) + self.ALIGN
+        world = dist.get_world_size(group)
+        self.mailbox_slice_bytes = int(mailbox_slice_bytes)
+        self.head = -(-_native.gather_block_bytes(world, self.mailbox_slice_bytes) // self.ALIGN) * self.ALIGN
+        self.bytes = int(nbytes) + self.head
         self.storage = symm.empty(self.bytes, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.storage, group)
         self.rank, self.world = int(self.handle.rank), int(self.handle.world_size)
@@ -71,7 +77,7 @@ class PeerArena:
         self.storage.zero_()                       # flag block: epochs, ticket and status start at zero
         torch.cuda.synchronize(device)
         dist.barrier(group=group)                  # nobody signals into a block that is not zeroed yet
-        self.used = self.ALIGN
+        self.used = self.head
         self.buffers = {}
 
     @property
@@ -180,7 +186,8 @@ class ColumnShardedLinear(torch.nn.Module):
         if self.local is not None and m > 0:
             self.local.forward_into(x, full[:, start:stop])
         if m > 0:
-            _native.gather(ptrs, self.arena.flag_ptrs, self.rank, m, self.out_features, start, stop - start)
+            _native.gather(ptrs, self.arena.flag_ptrs, self.arena.mailbox_slice_bytes, self.rank, m, self.out_features,
+                           self.out_features, self.rows_per_rank)
         return full
 
     def gather(self, y_local):

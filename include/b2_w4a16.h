@@ -238,24 +238,32 @@ int b2_w4a16_set_gemm_shape(int shape, int k_splits);
 
 /* Multi-GPU: all-gather of the column slices of an [M, N] FP16 output over NVLink.  No counterpart in
  * the reference, which is single-GPU; it is the collective step of the column-sharded layer (each rank
- * owns the output columns of its rows of W).  Every rank has its own copy of the [m, ld] buffer in memory
- * that all peers can write (peer-mapped / symmetric memory) and has written its slice
- * [col0, col0 + cols) into its own copy - the projection stores there directly.  The call pushes that
- * slice into every peer's copy with plain stores, then exchanges epoch flags: when the kernel ends, the
- * local copy holds every rank's slice.  One launch; nothing reads remote memory.
+ * owns the output columns of its rows of W).  Rank q owns the columns [q * slice_cols, min(n_total,
+ * (q + 1) * slice_cols)).  Every rank has its own copy of the [m, ld] buffer in memory that all peers can
+ * write (peer-mapped / symmetric memory) and has written its slice into its own copy - the projection
+ * stores there directly.  One launch; when the kernel ends, the local copy holds every rank's slice.
+ * Nothing reads remote memory, no TMA or bulk copy touches a peer, nothing is multicast.
  *   y_ranks[q], flag_blocks[q]  HOST arrays of `world` device pointers as mapped into this process
- *                               (entry [rank] is this rank's own); a flag block is
- *                               B2_GATHER_FLAG_BYTES of zero-initialised memory, one per rank and
- *                               process, shared by every gathered layer; all ranks must issue the same
- *                               sequence of gathers.
- * The wait for the peers is bounded (five seconds by default, b2_w4a16_gather_wait_limit): if a
- * peer's flag does not arrive, bit 2 of the flag block's status word is set (b2_w4a16_gather_status
- * reads it, synchronizing) and the kernel returns.  Reuse of one buffer: a peer may start writing the
- * next call's slice as soon as it has seen this rank's flag, so between two gathers into the SAME
- * buffer a rank must issue at least one other gather (or alternate two buffers). */
-#define B2_GATHER_FLAG_BYTES 128
-int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int rank, int world, int64_t m, int64_t ld,
-                    int64_t col0, int64_t cols, void* stream);
+ *                               (entry [rank] is this rank's own).  A flag block is
+ *                               b2_w4a16_gather_block_bytes(world, mailbox_slice_bytes) of zero-initialised,
+ *                               8-byte aligned memory, one per rank and process, shared by every gathered
+ *                               layer; all ranks must issue the same sequence of gathers with the same
+ *                               mailbox_slice_bytes.
+ * Two forms, chosen by size (the same way on every rank):
+ *   - a rank's slice (m * slice_cols * 2 bytes) fits in mailbox_slice_bytes and the slices are 4-byte
+ *     aligned: every word travels as an 8-byte packet {word, epoch} into the peer's mailbox, and the
+ *     receiving kernel polls the packets and copies the words into its buffer - one NVLink crossing, no
+ *     fence, ~5 us per gather (latency is all that matters at decode sizes);
+ *   - otherwise: the slice is pushed straight into every peer's buffer with 16-byte stores, then the last
+ *     CTA publishes this call's epoch in every peer's flag block (st.release.sys) and waits for theirs.
+ * Every wait is bounded by the clock (five seconds by default, b2_w4a16_gather_wait_limit): if a peer's data
+ * does not arrive, bit 2 of the flag block's status word is set (b2_w4a16_gather_status reads it,
+ * synchronizing) and the kernel returns.  Reuse of one buffer: a peer may start writing the next call's slice
+ * as soon as it has finished this call, so between two gathers into the SAME buffer a rank must issue at
+ * least one other gather (or alternate two buffers). */
+int64_t b2_w4a16_gather_block_bytes(int world, int64_t mailbox_slice_bytes);
+int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world,
+                    int64_t m, int64_t ld, int64_t n_total, int64_t slice_cols, void* stream);
 int b2_w4a16_gather_status(const void* flag_block, void* stream, unsigned* status_host);
 int b2_w4a16_gather_wait_limit(int64_t microseconds);      /* <= 0 restores the default */
 

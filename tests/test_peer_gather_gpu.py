@@ -16,26 +16,31 @@ import torch
 from dandan_ops_b200 import _native
 
 pytestmark = pytest.mark.gpu
-WORDS = _native.GATHER_FLAG_BYTES // 4
+MAILBOX = 1 << 16            # bytes of one slice that may travel as packets in these tests
 
 
-def _setup(m, n):
+def _setup(m, n, mailbox=0):
     bufs = [torch.full((m, n), float(r + 1), dtype=torch.float16, device="cuda") for r in range(2)]
-    flags = [torch.zeros(WORDS, dtype=torch.int32, device="cuda") for _ in range(2)]
+    words = _native.gather_block_bytes(2, mailbox) // 4
+    flags = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(2)]
     return bufs, flags
 
 
-@pytest.mark.parametrize("m,n,col0,cols", [(1, 1024, 0, 512), (8, 4096, 2048, 2048), (5, 1000, 504, 496), (3, 77, 13, 31),
-                                           (300, 12288, 6144, 6144)])
-def test_push_and_flag_exchange_with_a_host_played_peer(m, n, col0, cols):
+def _call(bufs, flags, mailbox, m, n_total, slice_cols):
+    _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], mailbox, 0, m, bufs[0].shape[1], n_total, slice_cols)
+
+
+@pytest.mark.parametrize("m,n,slice_cols", [(1, 1024, 512), (8, 4096, 2048), (5, 992, 496), (3, 62, 31), (300, 12288, 6144)])
+def test_push_and_flag_exchange_with_a_host_played_peer(m, n, slice_cols):
+    """Large-slice form (no mailbox): rank 0's columns [0, slice_cols) are pushed into the peer's buffer."""
     bufs, flags = _setup(m, n)
     g = torch.Generator().manual_seed(m + n)
-    bufs[0][:, col0:col0 + cols] = torch.randn(m, cols, generator=g).half().cuda()
+    bufs[0][:, :slice_cols] = torch.randn(m, slice_cols, generator=g).half().cuda()
     want = bufs[1].clone()
-    want[:, col0:col0 + cols] = bufs[0][:, col0:col0 + cols]
+    want[:, :slice_cols] = bufs[0][:, :slice_cols]
     for call in range(1, 4):                                  # epochs 1, 2, 3 on the same flag blocks
         flags[0][1] = call                                    # the peer's slice "has arrived"
-        _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 0, m, n, col0, cols)
+        _call(bufs, flags, 0, m, n, slice_cols)
         torch.cuda.synchronize()
         assert torch.equal(bufs[1], want)                     # slice pushed, nothing else touched
         assert int(flags[1][0]) == call                       # my epoch published in the peer's block
@@ -43,27 +48,59 @@ def test_push_and_flag_exchange_with_a_host_played_peer(m, n, col0, cols):
     assert _native.gather_status(flags[0].data_ptr()) == 0
 
 
-def test_a_peer_that_never_arrives_gives_a_status_not_a_hang():
-    bufs, flags = _setup(4, 256)
+def _mailbox_view(flag_block, parity, sender):
+    slots = MAILBOX // 4
+    box = flag_block[32:].view(2, 2, slots, 2)                # [parity][sender][slot]{word, epoch}
+    return box[parity, sender]
+
+
+@pytest.mark.parametrize("m,n,slice_cols", [(1, 1024, 512), (8, 4096, 2048), (16, 1000, 504), (5, 62, 32)])
+def test_mailbox_form_with_a_host_played_peer(m, n, slice_cols):
+    """Small-slice form: my words go out as {word, epoch} packets into the peer's mailbox, and the peer's
+    packets - written here by the host before the launch - are polled and copied into my buffer."""
+    bufs, flags = _setup(m, n, MAILBOX)
+    g = torch.Generator().manual_seed(3 * m + n)
+    cols1 = n - slice_cols
+    for call in range(1, 4):
+        mine = torch.randn(m, slice_cols, generator=g).half().cuda()
+        theirs = torch.randn(m, cols1, generator=g).half().cuda()
+        bufs[0][:, :slice_cols] = mine
+        packets = _mailbox_view(flags[0], call & 1, 1)
+        packets[:m * cols1 // 2, 0] = theirs.contiguous().view(torch.int32).reshape(-1)
+        packets[:m * cols1 // 2, 1] = call
+        _call(bufs, flags, MAILBOX, m, n, slice_cols)
+        torch.cuda.synchronize()
+        assert torch.equal(bufs[0][:, slice_cols:], theirs) and torch.equal(bufs[0][:, :slice_cols], mine)
+        sent = _mailbox_view(flags[1], call & 1, 0)[:m * slice_cols // 2]
+        assert torch.equal(sent[:, 0], mine.contiguous().view(torch.int32).reshape(-1)) and bool((sent[:, 1] == call).all())
+        assert int(flags[0][16]) == call and int(flags[0][17]) == 0 and int(flags[0][18]) == 0
+    assert _native.gather_status(flags[0].data_ptr()) == 0
+
+
+@pytest.mark.parametrize("mailbox", [0, MAILBOX])
+def test_a_peer_that_never_arrives_gives_a_status_not_a_hang(mailbox):
+    bufs, flags = _setup(4, 256, mailbox)
     _native.gather_wait_limit(2000)       # 2 ms
     try:
-        _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 0, 4, 256, 0, 128)
-        torch.cuda.synchronize()                               # returns although flags[0][1] stays 0
+        _call(bufs, flags, mailbox, 4, 256, 128)
+        torch.cuda.synchronize()                               # returns although nothing of the peer ever arrives
     finally:
         _native.gather_wait_limit(0)
     assert _native.gather_status(flags[0].data_ptr()) & 4
     assert int(flags[0][16]) == 1 and int(flags[0][17]) == 0   # epoch advanced, ticket reset: the block is reusable
-    assert torch.equal(bufs[1][:, :128], bufs[0][:, :128])
+    if mailbox == 0:
+        assert torch.equal(bufs[1][:, :128], bufs[0][:, :128])
 
 
 def test_gather_argument_checks():
     lib = _native.load()
     bufs, flags = _setup(2, 64)
-    with pytest.raises(RuntimeError, match="slice outside the row"):
-        _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 0, 2, 64, 32, 64)
+    with pytest.raises(RuntimeError, match="slices do not cover"):
+        _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 0, 0, 2, 64, 64, 16)
     with pytest.raises(RuntimeError, match="rank / world"):
-        _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 2, 2, 64, 0, 32)
+        _native.gather([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], 0, 2, 2, 64, 64, 32)
     assert lib.b2_w4a16_noop(None) == 0
+    assert _native.gather_block_bytes(8, 1 << 20) == 128 + 2 * 8 * (1 << 20) * 2
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
