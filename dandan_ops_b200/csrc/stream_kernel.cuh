@@ -58,8 +58,9 @@ __host__ __device__ constexpr int stream_x_bytes(int w) { return w == 16 ? w * 4
 // to 144 bytes and chunks by 32 more, which spreads the eight lanes of a quarter warp (two rows x
 // four chunks) over all eight 16-byte bank groups without any address arithmetic per piece.
 __host__ __device__ constexpr int stream_x_chunk_bytes(int rows) { return rows * 144 + 32; }
+constexpr int kStreamZeroBytes = 128;   // a row of zeros behind the x buffer: the B fragments of rows of x that do not exist
 __host__ __device__ constexpr int stream_smem_bytes(int w) {
-    return stream_bar_bytes(w) + stream_ring_bytes(w) + stream_x_bytes(w);
+    return stream_bar_bytes(w) + stream_ring_bytes(w) + stream_x_bytes(w) + kStreamZeroBytes;
 }
 constexpr unsigned kStatusCopyTimeout = 1u;
 constexpr int kWaitLimit = 1 << 20;          // mbarrier polls before a warp gives up
@@ -353,19 +354,20 @@ __device__ __forceinline__ void stage_wait() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
-// Stage x[0..MT*8) x [k0, k0 + cols) into shared memory (zero beyond M and K).
+// Stage x[0..rows) x [k0, k0 + cols) into shared memory (zero beyond M and K).  `rows` = MT * 8, or, in the
+// streaming kernel at MT = 1, only the rows of x that exist; `chunk` = stream_x_chunk_bytes(rows).
 template <int MT, bool XVEC, int W, bool WAIT = true>
-__device__ __forceinline__ void stage_x(uint8_t* xs, const StreamArgs& a, int k0, int cols) {
-    constexpr int MP = MT * 8;
-    // Work item = (row, column block): 32 pieces, one per lane, dealt to the warps in turn.  MP is a
-    // power of two, so the split of the item index needs no division (`cols` is a multiple of 256).
-    const int items = MP * (cols >> 8);
+__device__ __forceinline__ void stage_x(uint8_t* xs, const StreamArgs& a, int k0, int cols, int rows = MT * 8,
+                                        int chunk = stream_x_chunk_bytes(MT * 8)) {
+    // Work item = (row, column block): 32 pieces, one per lane, dealt to the warps in turn
+    // (`cols` is a multiple of 256).
+    const int items = rows * (cols >> 8);
     const int lane = threadIdx.x & 31;
     for (int it = threadIdx.x >> 5; it < items; it += W) {
-        const int m = it & (MP - 1), cc = (it / MP) * 32 + lane;
+        const int blk = it / rows, m = it - blk * rows, cc = blk * 32 + lane;
         const int T = cc >> 3, c = cc & 7;
         const int k = k0 + cc * 8;
-        stage_piece<XVEC>(xs + T * stream_x_chunk_bytes(MP) + m * 144 + c * 16, a.x + int64_t(m) * a.ldx + k,
+        stage_piece<XVEC>(xs + T * chunk + m * 144 + c * 16, a.x + int64_t(m) * a.ldx + k,
                           m < a.m && k < a.k, k, a.k);
     }
     if constexpr (WAIT) stage_wait();
@@ -385,9 +387,15 @@ w4a16_stream_kernel(const StreamArgs a) {
     constexpr int MP = MT * 8;
     constexpr int kWarps = W;
     constexpr int kBarBytes = stream_bar_bytes(W), kRingBytes = stream_ring_bytes(W);
-    constexpr int kChunk = stream_x_chunk_bytes(MP);
-    constexpr int kPhaseBlocks = stream_x_bytes(W) / (4 * kChunk);   // W=16: 16, 8, 4, 2 column blocks
-    static_assert(kPhaseBlocks >= 1, "x phase must hold at least one column block");
+    // Up to 8 rows of x only the rows that exist are staged (rows beyond M are zero B fragments, read from a
+    // 128-byte row of zeros): at M = 1 the x buffer then holds 118 column blocks instead of 16, so x is
+    // staged once per CTA for every K up to 30 000 and the CTA never stops for an x phase again.
+    const int xrows = MT == 1 ? a.m : MP;
+    // rows of 144 bytes, padded so that consecutive chunks sit 32 bytes apart modulo 128: the eight lanes of a
+    // quarter warp (two rows, four chunks) then read eight different 16-byte bank groups for any row count
+    const int kChunk = xrows * 144 + ((32 - xrows * 16) & 127);
+    const int kPhaseBlocks = stream_x_bytes(W) / (4 * kChunk);      // W=16, all rows staged: 16, 8, 4, 2 column blocks
+    static_assert(stream_x_bytes(W) / (4 * stream_x_chunk_bytes(MP)) >= 1, "x phase must hold at least one column block");
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -408,9 +416,13 @@ w4a16_stream_kernel(const StreamArgs a) {
 
     // When all of K fits in the x buffer it is staged once for the whole kernel: x does not
     // depend on the row group, so the CTA never has to stop between row groups again.  The
-    // copies are issued first and awaited after the weight requests, so both latencies overlap.
+    // copies are issued first and awaited after the weight requests, so both latencies overlap
+    // (the other order was measured 5 % slower on 24576 x 4096: every CTA reads the same lines of x,
+    // and that fan-in, not the weights' first trip, is the longer way at the start).
     const bool whole_x = a.kb <= kPhaseBlocks;
-    if (whole_x) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols);
+    uint8_t* xzero = xs + stream_x_bytes(W);
+    if (threadIdx.x < kStreamZeroBytes / 16) reinterpret_cast<uint4*>(xzero)[threadIdx.x] = make_uint4(0, 0, 0, 0);
+    if (whole_x) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols, xrows, kChunk);
 
     // Copy-request cursor (used by lane 0): image block (fkb, 16*fgrp + warp).  Consecutive
     // column blocks of one row tile are `stride` bytes apart; at the end of a row group the
@@ -468,7 +480,7 @@ w4a16_stream_kernel(const StreamArgs a) {
             const int p1 = min(k_hi, p0 + kPhaseBlocks);
             if (!whole_x) {
                 __syncthreads();                           // everyone is done with the previous x phase
-                stage_x<MT, XVEC, W>(xs, a, p0 * kBlockCols, (p1 - p0) * kBlockCols);
+                stage_x<MT, XVEC, W>(xs, a, p0 * kBlockCols, (p1 - p0) * kBlockCols, xrows, kChunk);
                 __syncthreads();
             }
             const int xorigin = whole_x ? 0 : p0;          // column block that the x buffer starts at
@@ -493,7 +505,7 @@ w4a16_stream_kernel(const StreamArgs a) {
                 if (++stage == kStages) { stage = 0; parity ^= 1u; }
 
                 const GroupConst<H16> gg = make_group<H16>(zero & 15u, step.x), gh = make_group<H16>(zero >> 4, step.y);
-                const uint8_t* xchunk = xs + ((kb - xorigin) * 4 + t) * kChunk + g * 144;
+                const uint8_t* xchunk = (MT > 1 || g < xrows) ? xs + ((kb - xorigin) * 4 + t) * kChunk + g * 144 : xzero;
 #pragma unroll
                 for (int wi = 0; wi < 8; ++wi) {
                     const uint32_t wa = pick(code[wi >> 2], wi & 3);        // row g
