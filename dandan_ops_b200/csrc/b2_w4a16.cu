@@ -14,6 +14,7 @@
 #include "layout_kernels.cuh"
 #include "stream_kernel.cuh"
 #include "stream2_kernel.cuh"
+#include "stream2d_kernel.cuh"
 #include "gemm_kernel.cuh"
 #include "gemm_pair_kernel.cuh"
 #include "tile_kernel.cuh"
@@ -82,7 +83,8 @@ std::atomic<int> g_wait_limit{b2::kWaitLimit};
 std::atomic<int> g_fault_step{-1};
 std::atomic<long long> g_gather_wait_ns{5000000000LL};   // five seconds
 std::atomic<int> g_stream_variant{0};     // 0/1 = w4a16_stream_kernel; 2 = w4a16_stream2_kernel with 32 warps wherever it applies;
-                                          // 3 = w4a16_stream2_kernel with 16 warps (M <= 16)
+                                          // 3 = w4a16_stream2_kernel with 16 warps (M <= 16);
+                                          // 4 = w4a16_stream2d_kernel (chunk-major split) wherever K exceeds the x buffer
 
 struct StreamPlan {
     int mt;            // 8-row tiles of x per launch: 1, 2, 4 or 8
@@ -93,7 +95,15 @@ struct StreamPlan {
     int grid;          // persistent CTAs
     int max_parts;     // most CTAs that share one row group
     int64_t partial_bytes;
+    int chunk_blocks;  // two-dimensional split (w4a16_stream2d_kernel): column blocks per K chunk, 0 = not used
+    int nchunks;
 };
+
+// Column blocks of x the streaming kernels' x buffer holds for `rows` staged rows (as the kernels compute it).
+int stream_x_blocks(int warps, int rows) {
+    const int chunk = rows * 144 + ((32 - rows * 16) & 127);
+    return b2::stream_x_bytes(warps) / (4 * chunk);
+}
 
 StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     StreamPlan p;
@@ -124,6 +134,24 @@ StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     p.max_parts = int(parts);
     const long long split_tiles = (long long)(p.groups < p.grid ? p.groups : p.grid) * p.warps;
     p.partial_bytes = p.grid > 1 ? split_tiles * p.max_parts * p.mt * 512 : 0;
+    // Two-dimensional split: when K does not fit in the x buffer, cut it into chunks that do and number the
+    // steps chunk-major, so that a CTA stages x once (w4a16_stream2d_kernel).  Every row tile then has a
+    // ticket and nchunks or a few more partial slots.
+    p.chunk_blocks = 0;
+    p.nchunks = 1;
+    const int xblocks = stream_x_blocks(16, p.mt == 1 ? p.rows : p.mt * 8);
+    // Measured 2-8 % behind the one-dimensional split on the 8B/70B projections (the fence + ticket round trip of
+    // every tile costs more than the x phases it removes), so it runs only when asked for (stream_variant 4).
+    if (p.warps == 16 && p.mt <= 2 && variant == 4 && d.kb > xblocks && p.grid > 1) {
+        const int nch = (d.kb + xblocks - 1) / xblocks;
+        const int cb = (d.kb + nch - 1) / nch;
+        if (nch <= 32 && (long long)p.groups * 16 <= ticket_slots && (d.kb + cb - 1) / cb == nch) {
+            p.chunk_blocks = cb;
+            p.nchunks = nch;
+            p.max_parts = int(nch * ((cb + per_cta - 1) / per_cta + 1));
+            p.partial_bytes = (long long)p.groups * 16 * p.max_parts * p.mt * 512;
+        }
+    }
     return p;
 }
 
@@ -162,9 +190,30 @@ int launch_stream2_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
     return after_launch("w4a16_stream2_kernel");
 }
 
+template <int MT, bool XVEC, bool H16>
+int launch_stream2d_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
+    auto kernel = b2::w4a16_stream2d_kernel<MT, XVEC, H16>;
+    constexpr int smem = b2::stream_smem_bytes(16);
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<grid, 16 * 32, smem, s>>>(a);
+    return after_launch("w4a16_stream2d_kernel");
+}
+
 template <int MT>
 int launch_stream(const b2::StreamArgs& a, bool xvec, int warps, int grid, cudaStream_t s, bool h16) {
     if constexpr (MT <= 2) {
+        if (a.nchunks > 1) {
+            if (h16 && xvec) return launch_stream2d_one<MT, true, true>(a, grid, s);
+            return xvec ? launch_stream2d_one<MT, true, false>(a, grid, s) : launch_stream2d_one<MT, false, false>(a, grid, s);
+        }
         // FP16-step chain: up to 16 rows of an aligned x (the decode case it was built for)
         if (h16 && xvec && warps == 16) return launch_stream_one<MT, true, 16, true>(a, grid, s);
         if (h16 && xvec && warps == 4) return launch_stream_one<MT, true, 4, true>(a, grid, s);
@@ -311,6 +360,7 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.m = int(rows); a.n = d.n; a.k = d.k;
         a.n16 = d.n16; a.kb = d.kb;
         a.groups = p.groups; a.max_parts = p.max_parts; a.steps = int(p.steps);
+        a.chunk_blocks = p.chunk_blocks; a.nchunks = p.nchunks;
         a.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
         a.fault_step = g_fault_step.exchange(-1, std::memory_order_relaxed);
         int rc;
@@ -596,7 +646,7 @@ const char* b2_w4a16_last_error(void) { return g_error.c_str(); }
 int64_t b2_w4a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int b2_w4a16_test_hooks(int wait_limit, int skip_copy, int stream_variant) {
-    if (stream_variant < 0 || stream_variant > 3) return fail(B2_ERR_ARGUMENT, "stream_variant must be 0..3");
+    if (stream_variant < 0 || stream_variant > 4) return fail(B2_ERR_ARGUMENT, "stream_variant must be 0..4");
     g_wait_limit.store(wait_limit > 0 ? wait_limit : b2::kWaitLimit, std::memory_order_relaxed);
     g_fault_step.store(skip_copy >= 0 ? skip_copy : -1, std::memory_order_relaxed);
     g_stream_variant.store(stream_variant, std::memory_order_relaxed);

@@ -81,6 +81,8 @@ struct StreamArgs {
                             //    y[:, 8*tile + g] = silu_mul(gate, up), y has n/2 columns
     int max_parts;          // partial slots per row tile
     int steps;              // groups * kb (below 2^20 for every layer the index checks admit)
+    int chunk_blocks;       // w4a16_stream2d_kernel: column blocks per K chunk (all chunks but the last)
+    int nchunks;            //   and the number of chunks (0 / 1 in the other kernels)
     int wait_limit;         // mbarrier polls before a warp gives up (kWaitLimit; a test passes a small number)
     int fault_step;         // -1; a test passes n >= 0: warp 0 of CTA 0 arms the barrier of its n-th weight
                             // copy but does not issue the copy, so that the wait for it runs out

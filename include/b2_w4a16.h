@@ -275,8 +275,8 @@ int b2_w4a16_noop(void* stream);
  * NEXT decode-kernel launch (tile or streaming) arms the barrier of that copy of its first CTA but does
  * not issue the copy, so the wait runs out, the warp records bit 0 in the status word, drains its other
  * copies and the kernel returns - nothing hangs; -1 = off.  stream_variant: 0 or 1 = the shipped
- * streaming kernel; 2 / 3 = the double-buffered form with 32 / 16 warps per CTA (M <= 16), kept for
- * measurements. */
+ * streaming kernel; 2 / 3 = the double-buffered form with 32 / 16 warps per CTA, 4 = the chunk-major
+ * two-dimensional split (all M <= 16), kept for measurements. */
 int b2_w4a16_test_hooks(int wait_limit, int skip_copy, int stream_variant);
 
 /* Number of kernels this library has launched from the calling process so far. */

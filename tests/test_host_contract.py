@@ -246,3 +246,22 @@ def test_operator_library_registers_the_reference_op_names():
         assert hasattr(torch.ops.dandan_ops, "w4a16_linear_image")
         schema = str(torch.ops.dandan_ops.w4a16_small.default._schema)
         assert "Tensor x, Tensor packed_w, Tensor scales, Tensor zeros, int group_size" in schema
+
+
+def test_stream_plan_keeps_tickets_inside_the_ticket_area():
+    """Host-only planning arithmetic: one arrival ticket per row tile of a split row group must fit in the
+    workspace's ticket area (its last word is the status word), whatever the layer's height, and the workspace
+    size grows with the partial tiles the plan needs."""
+    from dandan_ops_b200 import _native
+
+    lib = _native.load()
+    tickets = _native.TICKET_BYTES // 4 - 1
+    for n, k, m in ((200_000, 4096, 1), (1_000_000, 1024, 8), (131072, 8192, 16), (57344, 8192, 8), (8192, 28672, 1), (64, 64, 1)):
+        plan = _native.plan(m, n, k)
+        need = lib.b2_w4a16_workspace_bytes(m, n, k)
+        assert need >= _native.TICKET_BYTES
+        if plan["route"] == "b200_stream":
+            groups16 = -(-(-(-n // 16)) // 16)
+            if groups16 > plan["grid"]:                      # split row groups are indexed by CTA: grid * 16 tickets
+                assert plan["grid"] * 16 <= tickets, (n, k, m, plan)
+            assert plan["k_splits"] >= 1 and plan["grid"] >= 1

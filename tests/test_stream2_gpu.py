@@ -1,4 +1,8 @@
-"""The 32-warp streaming kernel (large layers, M <= 16) and the give-up path of the bounded waits.
+"""The other forms of the streaming kernel (large layers, M <= 16) and the give-up path of the bounded waits.
+
+Variant 0 / 1 is the shipped kernel (what B2_ROUTE_AUTO runs); 2 / 3 are the 32- / 16-warp double-buffered
+forms, 4 the chunk-major two-dimensional split (w4a16_stream2d_kernel) wherever K exceeds the x buffer - all
+measured slower or level, kept behind the hook.
 
 The 32-warp form is forced where the size rule would not pick it, so that ragged shapes (N not a
 multiple of 16 or 512, K not a multiple of 256 or 8, rows of x in 1..16) reach it; it is compared with
@@ -30,7 +34,7 @@ def _layer(n, k, seed):
     return ops.QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.02).half().cuda()), g
 
 
-@pytest.mark.parametrize("variant", [2, 3])
+@pytest.mark.parametrize("variant", [2, 3, 4])
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(5000, 8192), (12289, 4104), (16384, 2304), (9001, 8198), (4099, 28672)])
 def test_forced_32_warp_kernel_on_ragged_shapes(hooks, variant, m, n, k):
@@ -50,11 +54,13 @@ def test_forced_32_warp_kernel_on_ragged_shapes(hooks, variant, m, n, k):
 
 
 @pytest.mark.parametrize("n,k", [(600, 8192), (1030, 4104)])
-def test_32_warp_kernel_weights_bit_exact(hooks, n, k):
-    """One-hot rows of x read single weight columns: y[m, n] must equal fp16(w[n, col[m]]) exactly."""
+@pytest.mark.parametrize("variant", [4, 2])
+def test_32_warp_kernel_weights_bit_exact(hooks, variant, n, k):
+    """One-hot rows of x read single weight columns: y[m, n] must equal fp16(w[n, col[m]]) exactly
+    (variant 4: the two-dimensional split, which 16 rows of x and K = 4104 / 8192 select)."""
     layer, _ = _layer(n, k, 3 * n + k)
     w16 = layer.dequantize().half()
-    hooks(stream_variant=2)
+    hooks(stream_variant=variant)
     for base in (0, k - 16):
         cols = torch.arange(base, base + 16)
         x = torch.zeros(16, k, dtype=torch.float16)
@@ -69,7 +75,7 @@ def _raw_call(lib, x, image, y, ws, n, k, route):
                                      ws.numel(), torch.cuda.current_stream().cuda_stream, route)
 
 
-@pytest.mark.parametrize("route,variant,m,n,k", [(_native.ROUTE_STREAM, 2, 8, 8192, 8192), (_native.ROUTE_STREAM, 1, 4, 8192, 4096),
+@pytest.mark.parametrize("route,variant,m,n,k", [(_native.ROUTE_STREAM, 4, 8, 8192, 8192), (_native.ROUTE_STREAM, 2, 8, 8192, 8192), (_native.ROUTE_STREAM, 1, 4, 8192, 4096),
                                                  (_native.ROUTE_STREAM, 1, 40, 2048, 2048), (_native.ROUTE_TILE, 0, 8, 2048, 1024)])
 def test_a_wait_that_runs_out_sets_the_status_word_and_returns(hooks, route, variant, m, n, k):
     lib = _native.load()
