@@ -19,6 +19,7 @@
 #include "gemm_pair_kernel.cuh"
 #include "tile_kernel.cuh"
 #include "gather_kernel.cuh"
+#include "rmsnorm.cuh"
 
 namespace {
 
@@ -800,66 +801,16 @@ __global__ void silu_mul_pairs_kernel(const __half* in, int64_t ld_in, __half* o
     }
 }
 
-// Residual + RMSNorm: one CTA of eight warps per row.  The sum of squares is added in eight
-// lane-strided slices (one per warp), butterfly inside a slice, slices in order: a fixed order, so
-// results do not depend on the launch.  `summed` may alias nothing else; when null the sums pass
-// through `out`.
-__global__ void __launch_bounds__(32 * b2::kNormSlices)
+// Residual + RMSNorm: one CTA of eight warps per row (b2::norm_row, csrc/rmsnorm.cuh).  `summed` may alias
+// nothing else; when null the sums pass through `out`.
+__global__ void __launch_bounds__(b2::kNormThreads)
 residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, int64_t ldr,
                          const __half* weight, float eps, __half* summed, int64_t lds,
                          __half* out, int64_t ldo, int m, int k) {
-    __shared__ float slice[b2::kNormSlices];
-    __shared__ float inverse_shared;
+    __shared__ b2::NormScratch scratch;
     const int row = blockIdx.x;
-    const int pieces = k >> 3;
-    __half* sums = summed ? summed + row * lds : out + row * ldo;
-    constexpr int kStride = 32 * b2::kNormSlices, kBatch = 4;      // loads in flight per thread; the sum keeps the order of the pieces
-    float sq = 0.0f;
-    for (int c0 = threadIdx.x; c0 < pieces; c0 += kStride * kBatch) {
-        uint4 v[kBatch], r[kBatch];
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + kStride * j;
-            v[j] = cc < pieces ? __ldg(reinterpret_cast<const uint4*>(x + row * ldx + cc * 8)) : make_uint4(0, 0, 0, 0);
-            r[j] = (cc < pieces && residual) ? __ldg(reinterpret_cast<const uint4*>(residual + row * ldr + cc * 8)) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + kStride * j;
-            if (cc < pieces) {
-                if (residual) v[j] = b2::add_piece(v[j], r[j]);
-                *reinterpret_cast<uint4*>(sums + cc * 8) = v[j];
-                sq = b2::sumsq_piece(v[j], sq);
-            }
-        }
-    }
-    sq = b2::warp_sum(sq);
-    if ((threadIdx.x & 31) == 0) slice[threadIdx.x >> 5] = sq;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float total = 0.0f;
-#pragma unroll
-        for (int p = 0; p < b2::kNormSlices; ++p) total += slice[p];
-        inverse_shared = b2::inverse_rms(total, k, eps);
-    }
-    __syncthreads();
-    const float inverse = inverse_shared;
-    for (int c0 = threadIdx.x; c0 < pieces; c0 += kStride * kBatch) {      // every thread re-reads only what it wrote itself
-        uint4 v[kBatch], w[kBatch];
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + kStride * j;
-            if (cc < pieces) {
-                v[j] = *reinterpret_cast<const uint4*>(sums + cc * 8);
-                w[j] = __ldg(reinterpret_cast<const uint4*>(weight + cc * 8));
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-            const int cc = c0 + kStride * j;
-            if (cc < pieces) *reinterpret_cast<uint4*>(out + row * ldo + cc * 8) = b2::norm_piece(v[j], inverse, w[j]);
-        }
-    }
+    __half* o = out + row * ldo;
+    b2::norm_row(x + row * ldx, residual ? residual + row * ldr : nullptr, weight, eps, summed ? summed + row * lds : o, o, k, scratch);
     (void)m;
 }
 
@@ -962,7 +913,7 @@ int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, in
     const b2::Dims d = b2::make_dims(n, k);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (!xn_scratch) return fail(B2_ERR_ARGUMENT, "xn_scratch [M, K] is required");
-    residual_rms_norm_kernel<<<unsigned(m), 32 * b2::kNormSlices, 0, s>>>(
+    residual_rms_norm_kernel<<<unsigned(m), b2::kNormThreads, 0, s>>>(
         static_cast<const __half*>(x), ldx, static_cast<const __half*>(residual), ldr,
         static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
         static_cast<__half*>(xn_scratch), k, int(m), int(k));
@@ -984,7 +935,7 @@ int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual,
     if (ldx < k || ldo < k || (residual && ldr < k) || (summed && lds < k))
         return fail(B2_ERR_ARGUMENT, "leading dimension smaller than the row length");
     if (m > INT_MAX - 128 || k > INT_MAX - 64 || m * k > INT_MAX) return fail(B2_ERR_RANGE, "dimensions exceed the kernel index range");
-    residual_rms_norm_kernel<<<unsigned(m), 32 * b2::kNormSlices, 0, static_cast<cudaStream_t>(stream)>>>(
+    residual_rms_norm_kernel<<<unsigned(m), b2::kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(x), ldx, static_cast<const __half*>(residual), ldr,
         static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
         static_cast<__half*>(out), ldo, int(m), int(k));
