@@ -17,13 +17,15 @@
 //
 // Weights: every warp keeps a ring of kStages native blocks in shared memory, filled by
 // bulk asynchronous copies (cp.async.bulk, one 2336-byte copy per block, completion
-// counted on an mbarrier).  The copies need no registers, so the 16 warps of an SM hold
-// ~150 KB in flight.  A lane reads its 73 bytes of a landed block with conflict-free
-// 16-byte shared loads and immediately hands the slot back to the copy engine.
+// counted on an mbarrier).  The copies need no registers; with two slots per warp the 16
+// warps of an SM hold ~37 KB in flight and 37 KB being decoded.  A lane reads its 73 bytes of
+// a landed block with conflict-free 16-byte shared loads and immediately hands the slot back
+// to the copy engine.
 //
-// Activations: x for a phase of up to 4096 columns is staged in shared memory once per
-// CTA, laid out [64-column chunk][row][eight 16-byte pieces] with padded rows and chunks so
-// that the 16-byte read a lane makes for its MMA B fragments is conflict-free.
+// Activations: x for a phase of up to 33 column blocks (8448 columns; fewer when more than 8
+// rows are staged, more when fewer) is staged in shared memory once per CTA, laid out
+// [64-column chunk][row][eight 16-byte pieces] with padded rows and chunks so that the
+// 16-byte read a lane makes for its MMA B fragments is conflict-free.
 //
 // Dequantization keeps the reference's arithmetic exactly:
 //     w = fp16_rn( fp32(code - zero) * step_fp32 )
@@ -43,7 +45,7 @@
 namespace b2 {
 
 #ifndef B2_STREAM_STAGES
-#define B2_STREAM_STAGES 4
+#define B2_STREAM_STAGES 2
 #endif
 #ifndef B2_STREAM_CTAS16
 #define B2_STREAM_CTAS16 1
@@ -53,7 +55,15 @@ constexpr int kStages = B2_STREAM_STAGES;    // ring depth per warp
 // for layers with too few steps to feed 16-warp CTAs on every SM).
 __host__ __device__ constexpr int stream_bar_bytes(int w) { return w * kStages * 8; }
 __host__ __device__ constexpr int stream_ring_bytes(int w) { return w * kStages * kBlockBytes; }
-__host__ __device__ constexpr int stream_x_bytes(int w) { return w == 16 ? w * 4736 / B2_STREAM_CTAS16 : w * 4736; }   // 74 KB / 18.5 KB
+// x buffer: a 16-warp CTA (one per SM) takes everything the ring leaves of the 227 KB a CTA may have - with the
+// two-block rings 152 KB, i.e. 33 column blocks of 8 staged rows (K = 8448) or 16 of 16 rows; a 4-warp CTA
+// (four per SM) 18.5 KB.  Ring depth 2 against 4 was measured level at M = 1 and 3-6 % ahead at M = 8 / 16 on
+// the 70B-class layers: one block in flight per warp covers the copy latency (a warp spends ~1.7 us on a
+// block), and K = 8192 becomes resident in x at M = 8.
+__host__ __device__ constexpr int stream_x_bytes(int w) {
+    return w == 16 ? ((232448 - 1024 - w * B2_STREAM_STAGES * 8 - w * B2_STREAM_STAGES * kBlockBytes - 128) / 128) * 128 / B2_STREAM_CTAS16
+                   : w * 4736;
+}
 // Staged x: 64-column chunk T, row m, 16-byte piece c at T*chunk + m*144 + c*16.  Rows are padded
 // to 144 bytes and chunks by 32 more, which spreads the eight lanes of a quarter warp (two rows x
 // four chunks) over all eight 16-byte bank groups without any address arithmetic per piece.
