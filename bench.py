@@ -19,9 +19,11 @@ Workloads (N x K of synthetic projections, weights ~ N(0, sigma^2) quantized by
 QuantizedLinear.from_float(group_size=64), x ~ N(0,1) FP16):
   llama3-70b-mlp (default)  6 layers x {57344x8192, 8192x28672}, M in 1,8.  With N > 1 ranks every
                             layer's rows (output columns) are split over the ranks - strong scaling -
-                            and the output slices are gathered over NVLink inside the timed region
-                            (peer stores into symmetric memory, one launch per linear; --no-gather
-                            leaves the slices where they are)
+                            and the output slices are gathered over NVLink inside the timed region:
+                            projection and gather are ONE launch per linear (the streaming kernel sends
+                            every finished tile to the peers' mailboxes and collects theirs;
+                            --separate-gather runs the projection and then the gather kernel,
+                            --no-gather leaves the slices where they are)
   qwen3-8b-layer            3 layers x {6144x4096, 4096x4096, 24576x4096, 4096x12288}, M in 1,16
   qwen3-0.6b-decode         28 layers x {4096x1024, 1024x2048, 6144x1024, 1024x3072}, M in 1,2,4,8
 (the last two run one replica per rank at N > 1: weak scaling, no exchange)
@@ -327,6 +329,8 @@ def run_gpu(args, rank, world, local_rank):
             start = shard_rows(n_full, world, rank)[0] if spec["shard"] else 0
             sharded = (ColumnShardedLinear(layer, out_features=n_full, rank=rank, world_size=world).attach_arena(arena)
                        if gather_on else None)
+            if sharded is not None:
+                sharded.fuse_gather = not args.separate_gather
             for m in spec["ms"]:
                 calls.append({"m": m, "name": name, "n": n, "k": k, "layer": layer, "n_full": n_full, "start": start,
                               "li": li, "sharded": sharded})
@@ -510,8 +514,12 @@ def run_gpu(args, rank, world, local_rank):
                        "timing": "step replayed as one CUDA graph, CUDA events on the launching stream, max over ranks",
                        "partition": (f"rows of every layer split over {world} ranks" if spec["shard"] and world > 1 else
                                      "whole layers on every rank"),
-                       "gather": ("peer stores into symmetric memory + epoch flags, one launch per linear, inside the timed region"
-                                  if gather_on else None)},
+                       "gather": (None if not gather_on else
+                                  "inside the timed region; projection + gather launches per linear: " +
+                                  ", ".join(f"{c['name']} M={c['m']}: {c['sharded'].gather_launches(c['m'])}"
+                                            for c in calls if c["li"] == 0) +
+                                  " (1 = one kernel streams the weights, sends finished tiles to the peers' mailboxes as "
+                                  "{word, epoch} packets and collects theirs; 2 = projection, then the gather kernel)")},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / NOMINAL_HBM_GBS, 4),
                          "traffic": None if factor is None else round(step_weight_bytes / proj_launches * factor),
@@ -758,6 +766,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama3-70b-mlp")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-gather", action="store_true", help="sharded workload at N > 1: leave the output slices on their ranks")
+    ap.add_argument("--separate-gather", action="store_true",
+                    help="sharded workload at N > 1: projection and gather as two launches per linear instead of one")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-shape tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload-only", action="store_true", help="per-shape table for the chosen workload only")

@@ -29,6 +29,9 @@ _SIGNATURES = {
     "b2_w4a16_test_hooks": (_int, [_int, _int, _int]),
     "b2_w4a16_gather": (_int, [ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _int, _int, _i64, _i64, _i64, _i64, _vp]),
     "b2_w4a16_gather_block_bytes": (_i64, [_int, _i64]),
+    "b2_w4a16_linear_gather": (_int, [_vp, _i64, _vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _int, _int, _i64,
+                                      _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
+    "b2_w4a16_linear_gather_launches": (_int, [_i64, _i64, _i64, _i64, _int, _int, _i64]),
     "b2_w4a16_gather_status": (_int, [_vp, _vp, ctypes.POINTER(ctypes.c_uint)]),
     "b2_w4a16_gather_wait_limit": (_int, [_i64]),
     "b2_w4a16_noop": (_int, [_vp]),
@@ -126,6 +129,41 @@ def gather(y_ptrs, flag_ptrs, mailbox_slice_bytes, rank, m, ld, n_total, slice_c
     ys = (_vp * world)(*y_ptrs)
     fs = (_vp * world)(*flag_ptrs)
     _check(load().b2_w4a16_gather(ys, fs, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, _stream()))
+
+
+def linear_gather(x, image, k, y_ptrs, flag_ptrs, mailbox_slice_bytes, rank, ld, n_total, slice_cols, bias=None, flags=0):
+    """`b2_w4a16_linear_gather` on the current stream: this rank's slice of the projection and the all-gather
+    of every rank's slice into the `[m, ld]` buffers at `y_ptrs` - one launch at decode sizes, else the
+    projection followed by `b2_w4a16_gather`.  `image` (may be None for a rank without rows) holds the rows
+    [rank * slice_cols, ...) of W, `bias` those entries of the FP16 bias."""
+    lib = load()
+    world = len(y_ptrs)
+    m = x.shape[0]
+    if m == 0:
+        return
+    ys = (_vp * world)(*y_ptrs)
+    fs = (_vp * world)(*flag_ptrs)
+    stream = _stream()
+    cols = max(0, min(slice_cols, n_total - rank * slice_cols))
+    if image is None or cols == 0:
+        _check(lib.b2_w4a16_gather(ys, fs, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, stream))
+        return
+    device = x.device
+    key = (m, cols, k, device.index)
+    need = _need_cache.get(key)
+    if need is None:
+        need = _need_cache[key] = int(lib.b2_w4a16_workspace_bytes(m, cols, k))
+    ws = None if _private else _workspaces.get((device.index, stream))
+    if ws is None or ws.numel() < need:
+        ws = workspace(device, need)
+    _check(lib.b2_w4a16_linear_gather(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
+                                      bias.data_ptr() if bias is not None else None, ys, fs, mailbox_slice_bytes,
+                                      rank, world, m, ld, n_total, slice_cols, k, ws.data_ptr(), ws.numel(), stream, flags))
+
+
+def linear_gather_launches(m, n_total, slice_cols, k, rank, world, mailbox_slice_bytes):
+    """Kernels one `linear_gather` call launches: 1 = projection and gather fused, 2 = projection then gather."""
+    return int(load().b2_w4a16_linear_gather_launches(m, n_total, slice_cols, k, rank, world, mailbox_slice_bytes))
 
 
 def gather_status(flag_ptr):

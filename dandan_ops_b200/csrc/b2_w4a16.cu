@@ -174,6 +174,34 @@ int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
     return after_launch("w4a16_stream_kernel");
 }
 
+constexpr int kNotFused = -1000;            // internal: the fused projection + gather does not apply, use two launches
+
+// Projection + all-gather in one launch (w4a16_stream_gather_kernel).  Its CTAs wait for packets from other
+// GPUs, so the whole grid must be resident at once: checked against the occupancy the runtime reports.
+template <int MT, int W, bool H16>
+int launch_stream_gather_one(const b2::StreamArgs& a, const b2::GatherArgs& ga, int grid, int sms, cudaStream_t s) {
+    auto kernel = b2::w4a16_stream_gather_kernel<MT, W, H16>;
+    constexpr int smem = b2::stream_smem_bytes(W);
+    static std::atomic<uint64_t> configured{0};
+    static std::atomic<int> per_sm[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return kNotFused;
+    const uint64_t bit = 1ull << dev;
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        int blocks = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, W * 32, smem);
+        if (e != cudaSuccess) return cuda_fail("cudaOccupancyMaxActiveBlocksPerMultiprocessor", e);
+        per_sm[dev].store(blocks, std::memory_order_relaxed);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    if ((long long)grid > (long long)per_sm[dev].load(std::memory_order_relaxed) * sms) return kNotFused;
+    kernel<<<grid, W * 32, smem, s>>>(a, ga);
+    return after_launch("w4a16_stream_gather_kernel");
+}
+
 template <int MT, bool XVEC, int W>
 int launch_stream2_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
     auto kernel = b2::w4a16_stream2_kernel<MT, XVEC, W>;
@@ -340,7 +368,8 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
 
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
                const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s,
-               const DeviceInfo& dev, const void* bias, int act = 0, bool h16 = false) {
+               const DeviceInfo& dev, const void* bias, int act = 0, bool h16 = false,
+               const b2::GatherArgs* ga = nullptr) {
     const int64_t ticket_bytes = B2_W4A16_TICKET_BYTES;
     const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
     for (int64_t m0 = 0; m0 < m; m0 += B2_STREAM_MAX_M) {
@@ -365,6 +394,17 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
         a.fault_step = g_fault_step.exchange(-1, std::memory_order_relaxed);
         int rc;
+        if (ga) {
+            // one launch for projection and gather: 16 rows at most, aligned x, the shipped 16- or 4-warp kernel
+            if (!xvec || p.mt > 2 || (p.warps != 16 && p.warps != 4) || p.nchunks > 1 || act) return kNotFused;
+            const int sms = dev.sm_count > 0 ? dev.sm_count : 148;
+            if (p.mt == 1) {
+                if (p.warps == 16) return h16 ? launch_stream_gather_one<1, 16, true>(a, *ga, p.grid, sms, s) : launch_stream_gather_one<1, 16, false>(a, *ga, p.grid, sms, s);
+                return h16 ? launch_stream_gather_one<1, 4, true>(a, *ga, p.grid, sms, s) : launch_stream_gather_one<1, 4, false>(a, *ga, p.grid, sms, s);
+            }
+            if (p.warps == 16) return h16 ? launch_stream_gather_one<2, 16, true>(a, *ga, p.grid, sms, s) : launch_stream_gather_one<2, 16, false>(a, *ga, p.grid, sms, s);
+            return h16 ? launch_stream_gather_one<2, 4, true>(a, *ga, p.grid, sms, s) : launch_stream_gather_one<2, 4, false>(a, *ga, p.grid, sms, s);
+        }
         switch (p.mt) {
             case 1: rc = launch_stream<1>(a, xvec, p.warps, p.grid, s, h16); break;
             case 2: rc = launch_stream<2>(a, xvec, p.warps, p.grid, s, h16); break;
@@ -814,10 +854,50 @@ residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, i
     (void)m;
 }
 
+// Checked arguments of a gather call and which of its forms applies.
+struct GatherCall {
+    b2::GatherArgs a;
+    bool vec;        // 16-byte pieces (push form)
+    bool mailbox;    // every rank's slice fits in a mailbox half and is made of whole 4-byte words
+};
+
+int make_gather_call(void* const* y_ranks, void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world,
+                     int64_t m, int64_t ld, int64_t n_total, int64_t slice_cols, GatherCall& c) {
+    if (!y_ranks || !flag_blocks) return fail(B2_ERR_ARGUMENT, "null pointer");
+    if (world < 1 || world > b2::kGatherMaxRanks || rank < 0 || rank >= world)
+        return fail(B2_ERR_ARGUMENT, "rank / world out of range (at most 16 ranks)");
+    if (m < 0 || n_total < 0 || slice_cols <= 0 || ld < n_total || slice_cols * world < n_total || mailbox_slice_bytes < 0)
+        return fail(B2_ERR_ARGUMENT, "slices do not cover the row");
+    if (m > INT_MAX) return fail(B2_ERR_RANGE, "m exceeds the kernel index range");
+    const int64_t col0 = std::min(n_total, int64_t(rank) * slice_cols);
+    const int64_t cols = std::min(slice_cols, n_total - col0);
+    b2::GatherArgs& a = c.a;
+    bool vec = col0 % 8 == 0 && cols % 8 == 0 && ld % 8 == 0;
+    bool words = slice_cols % 2 == 0 && n_total % 2 == 0 && ld % 2 == 0;
+    for (int q = 0; q < b2::kGatherMaxRanks; ++q) {
+        a.y[q] = q < world ? static_cast<__half*>(y_ranks[q]) : nullptr;
+        a.flags[q] = q < world ? static_cast<unsigned*>(flag_blocks[q]) : nullptr;
+        if (q < world) {
+            if (!a.flags[q] || (!a.y[q] && m * n_total > 0)) return fail(B2_ERR_ARGUMENT, "null pointer");
+            if (reinterpret_cast<uintptr_t>(a.flags[q]) % 8 || reinterpret_cast<uintptr_t>(a.y[q]) % 2)
+                return fail(B2_ERR_ARGUMENT, "misaligned buffer");
+            vec = vec && reinterpret_cast<uintptr_t>(a.y[q]) % 16 == 0;
+            words = words && reinterpret_cast<uintptr_t>(a.y[q]) % 4 == 0;
+        }
+    }
+    a.rank = rank; a.world = world; a.m = int(m); a.ld = ld; a.col0 = col0; a.cols = cols;
+    a.n_total = n_total; a.slice_cols = slice_cols; a.slots = mailbox_slice_bytes / 4;
+    a.wait_ns = g_gather_wait_ns.load(std::memory_order_relaxed);
+    c.vec = vec;
+    c.mailbox = words && world > 1 && m * slice_cols * 2 <= mailbox_slice_bytes && m * slice_cols > 0;
+    return B2_OK;
+}
+
 // act = 1: rows g / g+8 of every 16-row tile are a gate/up pair and y gets n/2 columns.
 int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                 int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
-                int64_t workspace_bytes, void* stream, int route, int act, int flags = 0) {
+                int64_t workspace_bytes, void* stream, int route, int act, int flags = 0,
+                const b2::GatherArgs* ga = nullptr) {
     const bool h16 = (flags & B2_FLAG_FP16_STEPS) != 0;
     const void* bias = bias_fp16;
     if (bias && reinterpret_cast<uintptr_t>(bias) % 4) return fail(B2_ERR_ARGUMENT, "bias must be 4-byte aligned");
@@ -848,6 +928,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
             return fail(B2_ERR_UNSUPPORTED, "no fused gate/up epilogue for this problem: run b2_w4a16_linear, then b2_w4a16_silu_mul_pairs");
         route = B2_ROUTE_STREAM;
     }
+    if (ga && route != B2_ROUTE_STREAM) return kNotFused;     // only the streaming kernel carries the gather
     if (route == B2_ROUTE_TILE) {
         if (!tile_applicable(m, d, tile_split))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
@@ -856,7 +937,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
-                          static_cast<cudaStream_t>(stream), dev, bias, act, h16);
+                          static_cast<cudaStream_t>(stream), dev, bias, act, h16, ga);
     if (route == B2_ROUTE_TCGEN05) {
         if (!gemm_applicable(x, ldx, d))
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
@@ -1005,47 +1086,64 @@ int64_t b2_w4a16_gather_block_bytes(int world, int64_t mailbox_slice_bytes) {
 
 int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world,
                     int64_t m, int64_t ld, int64_t n_total, int64_t slice_cols, void* stream) {
-    if (!y_ranks || !flag_blocks) return fail(B2_ERR_ARGUMENT, "null pointer");
-    if (world < 1 || world > b2::kGatherMaxRanks || rank < 0 || rank >= world)
-        return fail(B2_ERR_ARGUMENT, "rank / world out of range (at most 16 ranks)");
-    if (m < 0 || n_total < 0 || slice_cols <= 0 || ld < n_total || slice_cols * world < n_total || mailbox_slice_bytes < 0)
-        return fail(B2_ERR_ARGUMENT, "slices do not cover the row");
-    if (m > INT_MAX) return fail(B2_ERR_RANGE, "m exceeds the kernel index range");
-    const int64_t col0 = std::min(n_total, int64_t(rank) * slice_cols);
-    const int64_t cols = std::min(slice_cols, n_total - col0);
-    b2::GatherArgs a;
-    bool vec = col0 % 8 == 0 && cols % 8 == 0 && ld % 8 == 0;
-    bool words = slice_cols % 2 == 0 && n_total % 2 == 0 && ld % 2 == 0;
-    for (int q = 0; q < b2::kGatherMaxRanks; ++q) {
-        a.y[q] = q < world ? static_cast<__half*>(y_ranks[q]) : nullptr;
-        a.flags[q] = q < world ? static_cast<unsigned*>(flag_blocks[q]) : nullptr;
-        if (q < world) {
-            if (!a.flags[q] || (!a.y[q] && m * n_total > 0)) return fail(B2_ERR_ARGUMENT, "null pointer");
-            if (reinterpret_cast<uintptr_t>(a.flags[q]) % 8 || reinterpret_cast<uintptr_t>(a.y[q]) % 2)
-                return fail(B2_ERR_ARGUMENT, "misaligned buffer");
-            vec = vec && reinterpret_cast<uintptr_t>(a.y[q]) % 16 == 0;
-            words = words && reinterpret_cast<uintptr_t>(a.y[q]) % 4 == 0;
-        }
-    }
-    a.rank = rank; a.world = world; a.m = int(m); a.ld = ld; a.col0 = col0; a.cols = cols;
-    a.n_total = n_total; a.slice_cols = slice_cols; a.slots = mailbox_slice_bytes / 4;
-    a.wait_ns = g_gather_wait_ns.load(std::memory_order_relaxed);
+    GatherCall c;
+    if (int rc = make_gather_call(y_ranks, flag_blocks, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, c)) return rc;
+    const b2::GatherArgs& a = c.a;
     DeviceInfo dev;
     if (int rc = device_info(dev)) return rc;
     const int sms = dev.sm_count > 0 ? dev.sm_count : 148;
     // Small slices (every rank's fits in a mailbox half): packets polled by the receiver, one NVLink crossing.
-    if (words && world > 1 && m * slice_cols * 2 <= mailbox_slice_bytes && m * slice_cols > 0) {
+    if (c.mailbox) {
         const int64_t items = m * (slice_cols / 2) * (world - 1);
         const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>((items + 255) / 256, 2LL * sms)));
         b2::gather_mailbox_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
         return after_launch("gather_mailbox_kernel");
     }
-    const int64_t items = m * (vec ? cols / 8 : cols) * (world - 1);
+    const int64_t items = m * (c.vec ? a.cols / 8 : a.cols) * (world - 1);
     const int64_t want = (items + 255) / 256;
     const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(want, 2LL * sms)));
-    if (vec) b2::gather_push_wait_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    if (c.vec) b2::gather_push_wait_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
     else b2::gather_push_wait_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
     return after_launch("gather_push_wait_kernel");
+}
+
+int b2_w4a16_linear_gather(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* const* y_ranks,
+                           void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world, int64_t m,
+                           int64_t ld, int64_t n_total, int64_t slice_cols, int64_t k, void* workspace,
+                           int64_t workspace_bytes, void* stream, int flags) {
+    if (flags & ~B2_FLAG_FP16_STEPS) return fail(B2_ERR_ARGUMENT, "unknown flag");
+    GatherCall c;
+    if (int rc = make_gather_call(y_ranks, flag_blocks, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, c)) return rc;
+    if (m == 0) return B2_OK;
+    const int64_t cols = c.a.cols;
+    if (cols > 0) {
+        void* y_local = static_cast<__half*>(y_ranks[rank]) + c.a.col0;
+        int rc = kNotFused;
+        if (c.mailbox && m <= 16) rc = linear_impl(x, ldx, native, bias_fp16, y_local, ld, m, cols, k, workspace, workspace_bytes,
+                                                   stream, B2_ROUTE_AUTO, 0, flags, &c.a);
+        if (rc != kNotFused) return rc;
+        rc = linear_impl(x, ldx, native, bias_fp16, y_local, ld, m, cols, k, workspace, workspace_bytes, stream,
+                         B2_ROUTE_AUTO, 0, flags);
+        if (rc != B2_OK) return rc;
+    }
+    return b2_w4a16_gather(y_ranks, flag_blocks, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, stream);
+}
+
+int b2_w4a16_linear_gather_launches(int64_t m, int64_t n_total, int64_t slice_cols, int64_t k, int rank, int world,
+                                    int64_t mailbox_slice_bytes) {
+    if (m <= 0 || world < 1 || rank < 0 || rank >= world || slice_cols <= 0) return 0;
+    const int64_t col0 = std::min(n_total, int64_t(rank) * slice_cols);
+    const int64_t cols = std::min(slice_cols, n_total - col0);
+    if (cols <= 0) return 1;                                   // nothing to compute: the gather alone
+    if (check_dims(cols, k) != B2_OK) return 0;
+    const bool mailbox = slice_cols % 2 == 0 && n_total % 2 == 0 && world > 1 && m * slice_cols * 2 <= mailbox_slice_bytes;
+    if (!mailbox || m > 16 || k % 8 != 0) return 2;
+    DeviceInfo dev;
+    if (device_info(dev) != B2_OK) dev.sm_count = 148;
+    const b2::Dims d = b2::make_dims(cols, k);
+    if (tile_applicable(m, d, tile_ksplit(d, dev.sm_count, pair_available()))) return 2;
+    const StreamPlan p = plan_stream(m, d, dev.sm_count);
+    return (p.warps == 16 || p.warps == 4) && p.nchunks <= 1 ? 1 : 2;
 }
 
 int b2_w4a16_gather_status(const void* flag_block, void* stream, unsigned* status_host) {

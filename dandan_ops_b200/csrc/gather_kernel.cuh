@@ -133,29 +133,18 @@ __device__ __forceinline__ uint2* mailbox(unsigned* flag_block, int world, int64
            (int64_t(parity) * world + sender) * slots;
 }
 
-__global__ void __launch_bounds__(256)
-gather_mailbox_kernel(const GatherArgs a) {
-    __shared__ int is_last;
+// One packet: the data word and the epoch of the call it belongs to, in one single-copy-atomic 8-byte store.
+__device__ __forceinline__ void mailbox_send(uint2* slot, unsigned data, unsigned epoch) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(slot), "r"(data), "r"(epoch) : "memory");
+}
+
+// Receiving half of the mailbox form: thread `first` of `stride` polls its share of the packets of every
+// peer's slice (bounded by the clock and by a poll count) and copies the words into the local buffer.
+// Returns true when a packet did not arrive in time.
+__device__ __forceinline__ bool mailbox_receive(const GatherArgs& a, unsigned epoch, int64_t first, int64_t stride) {
     unsigned* mine = a.flags[a.rank];
-    const unsigned epoch = *reinterpret_cast<volatile unsigned*>(mine + kGatherEpochWord) + 1u;
-    const unsigned parity = epoch & 1u;
     __half* y = a.y[a.rank];
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x, first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    // ---- send: every word of my slice to every peer's mailbox --------------------------------------
-    {
-        const int64_t wpr = a.cols >> 1;                                  // 4-byte words per row of my slice
-        const int64_t words = int64_t(a.m) * wpr;
-        const int peers = a.world - 1;
-        for (int64_t i = first; i < words * peers; i += stride) {
-            const int pi = int(i / words);
-            const int64_t s = i - pi * words;
-            const int64_t row = s / wpr, w = s - row * wpr;
-            const unsigned data = *reinterpret_cast<const unsigned*>(y + row * a.ld + a.col0 + 2 * w);
-            uint2* box = mailbox(a.flags[pi < a.rank ? pi : pi + 1], a.world, a.slots, parity, a.rank);
-            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(box + s), "r"(data), "r"(epoch) : "memory");
-        }
-    }
-    // ---- receive: poll the packets of every peer's slice and copy the words into my buffer ---------
+    const unsigned parity = epoch & 1u;
     bool gave_up = false;
     for (int q = 0; q < a.world; ++q) {
         if (q == a.rank) continue;
@@ -180,14 +169,48 @@ gather_mailbox_kernel(const GatherArgs a) {
             *reinterpret_cast<unsigned*>(y + row * a.ld + col0 + 2 * w) = data;
         }
     }
+    return gave_up;
+}
+
+// End of a mailbox call (every thread of every CTA calls it): record a timeout, count the CTA, and let the
+// last CTA of the grid publish the new epoch and re-zero the ticket.
+__device__ __forceinline__ void mailbox_finish(const GatherArgs& a, unsigned epoch, bool gave_up) {
+    unsigned* mine = a.flags[a.rank];
     if (gave_up) atomicOr(mine + kGatherStatusWord, kStatusPeerTimeout);
     __syncthreads();
-    if (threadIdx.x == 0) is_last = atomicAdd(mine + kGatherTicketWord, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (is_last && threadIdx.x == 0) {
+    if (threadIdx.x == 0 && atomicAdd(mine + kGatherTicketWord, 1u) == gridDim.x - 1) {
         mine[kGatherEpochWord] = epoch;
         mine[kGatherTicketWord] = 0u;
     }
+}
+
+// The epoch of the running call.  Any thread may read it at any time before its CTA has counted itself in
+// mailbox_finish: the word changes only after the last CTA of the grid has done so.
+__device__ __forceinline__ unsigned mailbox_epoch(const GatherArgs& a) {
+    return *reinterpret_cast<volatile unsigned*>(a.flags[a.rank] + kGatherEpochWord) + 1u;
+}
+
+__global__ void __launch_bounds__(256)
+gather_mailbox_kernel(const GatherArgs a) {
+    const unsigned epoch = mailbox_epoch(a);
+    const unsigned parity = epoch & 1u;
+    const __half* y = a.y[a.rank];
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x, first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    // ---- send: every word of my slice to every peer's mailbox --------------------------------------
+    {
+        const int64_t wpr = a.cols >> 1;                                  // 4-byte words per row of my slice
+        const int64_t words = int64_t(a.m) * wpr;
+        const int peers = a.world - 1;
+        for (int64_t i = first; i < words * peers; i += stride) {
+            const int pi = int(i / words);
+            const int64_t s = i - pi * words;
+            const int64_t row = s / wpr, w = s - row * wpr;
+            const unsigned data = *reinterpret_cast<const unsigned*>(y + row * a.ld + a.col0 + 2 * w);
+            mailbox_send(mailbox(a.flags[pi < a.rank ? pi : pi + 1], a.world, a.slots, parity, a.rank) + s, data, epoch);
+        }
+    }
+    // ---- receive: poll the packets of every peer's slice and copy the words into my buffer ---------
+    mailbox_finish(a, epoch, mailbox_receive(a, epoch, first, stride));
 }
 
 }  // namespace b2

@@ -41,6 +41,7 @@
 // exit (its outputs are then undefined; the host reads the status word on demand).
 #pragma once
 #include "layout.cuh"
+#include "gather_kernel.cuh"
 
 namespace b2 {
 
@@ -392,9 +393,17 @@ __device__ __forceinline__ int owner_of(int s, int steps, int ctas) {
 
 // MT = number of 8-row tiles of x (1, 2, 4 or 8).  XVEC: x rows are 16-byte aligned and
 // K is a multiple of 8, so x is read with 16-byte loads.
-template <int MT, bool XVEC, int W, bool H16 = false>
-__global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
-w4a16_stream_kernel(const StreamArgs a) {
+// GATHER: the multi-GPU form.  `a.y` is this rank's column slice of a full [M, N] buffer that every rank
+// holds (GatherArgs, csrc/gather_kernel.cuh).  The warp that completes a row tile stores it into the local
+// buffer AND sends it to every peer's mailbox as {word, epoch} packets (plain peer stores over NVLink, as
+// soon as the tile is done - the transfer overlaps the rest of the stream); a CTA that has finished its
+// range polls its share of the packets the peers sent and copies them into the local buffer.  When the
+// kernel ends the local buffer holds all slices: projection and all-gather in one launch.  Nothing reads a
+// peer's memory; every wait is bounded (status bit 2 of the flag block on a timeout).  A CTA waits only for
+// packets of OTHER GPUs, whose senders never wait before they send, so the launch needs no co-residency
+// with anything but its own grid (the host checks that the whole grid fits on the device at once).
+template <int MT, bool XVEC, int W, bool H16, bool GATHER>
+__device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArgs* ga) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MP = MT * 8;
     constexpr int kWarps = W;
@@ -579,7 +588,33 @@ w4a16_stream_kernel(const StreamArgs a) {
                     write_out = true;
                 }
             }
-            if (write_out) {
+            if (GATHER && write_out) {
+                // Lanes g and g ^ 1 exchange one value each, so that every lane holds the two neighbouring
+                // columns of one row as a 4-byte word: the unit of the local store and of a packet.
+                const unsigned epoch = mailbox_epoch(*ga);
+                const int64_t wpr = ga->cols >> 1;
+                const bool even = (g & 1) == 0;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int m0 = mt * 8 + 2 * t;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int n = nt * 16 + g + 8 * h;
+                        const unsigned v0 = (m0 < a.m && n < a.n) ? __half_as_ushort(finish_output(acc[mt][2 * h], a.bias, n)) : 0u;
+                        const unsigned v1 = (m0 + 1 < a.m && n < a.n) ? __half_as_ushort(finish_output(acc[mt][2 * h + 1], a.bias, n)) : 0u;
+                        const unsigned got = __shfl_xor_sync(0xffffffffu, even ? v1 : v0, 4);
+                        const int row = even ? m0 : m0 + 1, col = even ? n : n - 1;
+                        const unsigned word = even ? (v0 | (got << 16)) : (got | (v1 << 16));
+                        if (row < a.m && col < a.n) {
+                            *reinterpret_cast<unsigned*>(a.y + int64_t(row) * a.ldy + col) = word;
+                            const int64_t s = int64_t(row) * wpr + (col >> 1);
+                            for (int q = 0; q < ga->world; ++q)
+                                if (q != ga->rank)
+                                    mailbox_send(mailbox(ga->flags[q], ga->world, ga->slots, epoch & 1u, ga->rank) + s, word, epoch);
+                        }
+                    }
+                }
+            } else if (write_out) {
                 const int n0 = nt * 16 + g;
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
@@ -614,6 +649,24 @@ w4a16_stream_kernel(const StreamArgs a) {
             if (++stage == kStages) { stage = 0; parity ^= 1u; }
         }
     }
+
+    if constexpr (GATHER) {
+        const unsigned epoch = mailbox_epoch(*ga);
+        const int64_t threads = int64_t(gridDim.x) * blockDim.x;
+        mailbox_finish(*ga, epoch, mailbox_receive(*ga, epoch, int64_t(blockIdx.x) * blockDim.x + threadIdx.x, threads));
+    }
+}
+
+template <int MT, bool XVEC, int W, bool H16 = false>
+__global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
+w4a16_stream_kernel(const StreamArgs a) {
+    stream_body<MT, XVEC, W, H16, false>(a, nullptr);
+}
+
+template <int MT, int W, bool H16>
+__global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
+w4a16_stream_gather_kernel(const StreamArgs a, const GatherArgs ga) {
+    stream_body<MT, true, W, H16, true>(a, &ga);
 }
 
 }  // namespace b2

@@ -312,6 +312,16 @@ class QuantizedLinear(torch.nn.Module):
             self._checked_key, self._checked_device = self._forward_key(), self.packed_weight.device
         return y
 
+    def check_input(self, x):
+        """Metadata checks of the raw-kernel entry points (`forward_into`, the sharded layer's fused call):
+        CUDA FP16 `[M, in_features]`; returns x with unit inner stride."""
+        if type(x) is not torch.Tensor or x.dtype is not torch.float16 or x.ndim != 2 or x.shape[1] != self.in_features:
+            raise ValueError("x must be a CUDA FP16 tensor [M, in_features]")
+        _resolve(x, self.scales, self.group_size, self.backend)
+        if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < self.in_features):
+            x = x.contiguous()
+        return x
+
     def forward_into(self, x, out):
         """`forward(x)` written into `out`, an FP16 `[M, N]` CUDA tensor or a column slice of a wider one
         (unit inner stride; the row stride is passed to the kernel).  Used by the column-sharded layer,
@@ -319,11 +329,7 @@ class QuantizedLinear(torch.nn.Module):
         if (out.dtype != torch.float16 or out.ndim != 2 or tuple(out.shape) != (x.shape[0], self.out_features)
                 or out.stride(1) != 1 or out.device != x.device):
             raise ValueError("out must be an FP16 [M, N] tensor with unit inner stride on the input device")
-        if type(x) is not torch.Tensor or x.dtype is not torch.float16 or x.ndim != 2 or x.shape[1] != self.in_features:
-            raise ValueError("x must be a CUDA FP16 tensor [M, in_features]")
-        _resolve(x, self.scales, self.group_size, self.backend)
-        if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) < self.in_features):
-            x = x.contiguous()
+        x = self.check_input(x)
         image = self._native_image()
         return _native.linear(x, image, self.out_features, self.in_features, out=out, bias=self._bias_fp16(),
                               flags=self._image_flags)

@@ -120,6 +120,7 @@ class ColumnShardedLinear(torch.nn.Module):
         self.rows = (start, stop)
         self.rows_per_rank = shard_rows(out_features, world_size, 0)[1]
         self.arena = None
+        self.fuse_gather = True      # one launch for projection + gather where the library has it; False = always two
         self._calls = 0
 
     def attach_arena(self, arena):
@@ -175,20 +176,42 @@ class ColumnShardedLinear(torch.nn.Module):
         return self.gather(y) if gather else y
 
     def _forward_peer_gather(self, x):
-        """Projection into this rank's columns of the symmetric `[M, N]` buffer, then one
-        `b2_w4a16_gather` launch.  Two buffers per batch size are used in turn, so a peer that runs
+        """`b2_w4a16_linear_gather`: at decode sizes ONE launch that streams this rank's weights, sends every
+        finished tile to the peers' mailboxes and collects theirs; otherwise the projection into this rank's
+        columns of the symmetric `[M, N]` buffer followed by one `b2_w4a16_gather` launch.
+        Two buffers per batch size are used in turn, so a peer that runs
         ahead writes the next call's slice into the other buffer while this rank still reads this one
         (a captured graph replays the buffer it was captured with: see include/b2_w4a16.h)."""
         m = x.shape[0]
         full, ptrs = self.arena.output((id(self), self._calls & 1), m, self.out_features)
         self._calls += 1
-        start, stop = self.rows
-        if self.local is not None and m > 0:
-            self.local.forward_into(x, full[:, start:stop])
-        if m > 0:
-            _native.gather(ptrs, self.arena.flag_ptrs, self.arena.mailbox_slice_bytes, self.rank, m, self.out_features,
-                           self.out_features, self.rows_per_rank)
+        if m == 0:
+            return full
+        local = self.local
+        if local is not None and not self.fuse_gather:
+            start, stop = self.rows
+            local.forward_into(x, full[:, start:stop])
+            local = None                                   # the call below is then the gather alone
+        if local is None:
+            _native.linear_gather(x, None, 0, ptrs, self.arena.flag_ptrs, self.arena.mailbox_slice_bytes, self.rank,
+                                  self.out_features, self.out_features, self.rows_per_rank)
+            return full
+        x = local.check_input(x)
+        _native.linear_gather(x, local._native_image(), local.in_features, ptrs, self.arena.flag_ptrs,
+                              self.arena.mailbox_slice_bytes, self.rank, self.out_features, self.out_features,
+                              self.rows_per_rank, bias=local._bias_fp16(), flags=local._image_flags)
         return full
+
+    def gather_launches(self, m):
+        """Kernels one gathered forward of `m` rows launches on this rank (1 = projection and gather fused)."""
+        if self.arena is None or self.world_size == 1:
+            return None
+        if self.local is None:
+            return 1
+        if not self.fuse_gather:
+            return 2
+        return _native.linear_gather_launches(m, self.out_features, self.rows_per_rank, self.local.in_features, self.rank,
+                                              self.world_size, self.arena.mailbox_slice_bytes)
 
     def gather(self, y_local):
         """All-gather of the per-rank slices into `[M, N]` (same result on every rank)."""

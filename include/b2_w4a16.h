@@ -267,6 +267,25 @@ int b2_w4a16_gather(void* const* y_ranks, void* const* flag_blocks, int64_t mail
 int b2_w4a16_gather_status(const void* flag_block, void* stream, unsigned* status_host);
 int b2_w4a16_gather_wait_limit(int64_t microseconds);      /* <= 0 restores the default */
 
+/* Column-sharded projection and all-gather as ONE call: y_ranks[rank][:, :n_total] = x W^T (+bias) on every
+ * rank, where this rank's `native` image holds its rows [rank * slice_cols, min(n_total, (rank + 1) *
+ * slice_cols)) of W and `bias_fp16` (optional) those entries of the bias.  Arguments as b2_w4a16_gather and
+ * b2_w4a16_linear_flags; `ld` is the row stride of the gathered buffers.
+ * Decode sizes (m <= 16, a slice that fits a mailbox half, K % 8 == 0, an aligned x, a layer the streaming
+ * kernel takes) run as one launch, w4a16_stream_gather_kernel: the warp that completes a 16-column tile stores it
+ * into the local buffer and sends it to every peer's mailbox as {word, epoch} packets while the rest of the
+ * weight stream is still running; CTAs that have finished their range poll the packets the peers sent.
+ * The transfer overlaps the math tile by tile and the launch, fence and flag round trip of a separate gather
+ * disappear.  Everything else runs the projection (b2_w4a16_linear_flags into the local slice) followed by
+ * b2_w4a16_gather - same result, two launches; b2_w4a16_linear_gather_launches() says which (0 = bad arguments).
+ * All ranks must make the same sequence of calls; waits are bounded as in b2_w4a16_gather. */
+int b2_w4a16_linear_gather(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* const* y_ranks,
+                           void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world, int64_t m,
+                           int64_t ld, int64_t n_total, int64_t slice_cols, int64_t k, void* workspace,
+                           int64_t workspace_bytes, void* stream, int flags);
+int b2_w4a16_linear_gather_launches(int64_t m, int64_t n_total, int64_t slice_cols, int64_t k, int rank, int world,
+                                    int64_t mailbox_slice_bytes);
+
 /* Launches an empty kernel on `stream`: the floor of one graph node, for benchmarks. */
 int b2_w4a16_noop(void* stream);
 

@@ -3,9 +3,10 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node=N --master-addr 127.0.0.1 tests/multi_gpu_gather_check.py
 
 Every rank builds its row slice of a seeded layer (ColumnShardedLinear), attaches a PeerArena and runs
-forward(gather=True) - projection into the symmetric buffer + one b2_w4a16_gather launch - for decode
-and prefill batch sizes.  The gathered [M, N] must equal, bit for bit, the NCCL all-gather of the same
-local slices on every rank, must satisfy |y - y_ref| <= 2e-3 + 2e-3|y_ref| against the CPU oracle on
+forward(gather=True) - b2_w4a16_linear_gather: one launch that computes, sends and collects at decode
+sizes on layers the streaming kernel takes, else the projection into the symmetric buffer + one
+b2_w4a16_gather launch - for decode and prefill batch sizes, with and without the one-launch form.
+The gathered [M, N] must equal, bit for bit, the NCCL all-gather of the same local slices on every rank, must satisfy |y - y_ref| <= 2e-3 + 2e-3|y_ref| against the CPU oracle on
 rank 0, and a CUDA-graph capture of the gathered forward must replay to the same bits.
 """
 import os
@@ -32,7 +33,7 @@ def main():
     dist.init_process_group("nccl", device_id=device)
     arena = PeerArena(64 << 20)
     worst = 0.0
-    for n, k, with_bias in ((4096, 2048, False), (1000, 1032, True), (8192, 4096, False)):
+    for n, k, with_bias in ((4096, 2048, False), (1000, 1032, True), (8192, 4096, False), (2048, 28672, True)):
         g = torch.Generator().manual_seed(n + k)
         w = (torch.randn(n, k, generator=g) * 0.02).half()
         bias = torch.randn(n, generator=g) if with_bias else None
@@ -50,6 +51,12 @@ def main():
             xg = x.to(device)
             full = layer(xg, gather=True).clone()
             nccl = layer.gather(layer(xg))
+            if k == 28672 and m <= 16:
+                assert layer.gather_launches(m) == 1, "expected the one-launch form here"
+            layer.fuse_gather = False                          # the same through projection + gather kernel
+            two = layer(xg, gather=True).clone()
+            layer.fuse_gather = True
+            assert torch.equal(two, full), f"one-launch and two-launch forms differ (rank {rank}, {n}x{k}, M={m})"
             if not torch.equal(full, nccl):
                 start, stop = layer.rows
                 bad = (full != nccl)
