@@ -4,6 +4,7 @@ The library is the only compute path of the package: if it cannot be loaded, eve
 operation that needs it raises ImportError - there is no eager or CPU stand-in.
 """
 import ctypes
+import os
 import threading
 
 import torch
@@ -338,6 +339,8 @@ def linear_static(x, image, n, k, out):
 
 
 FLAG_FP16_STEPS = 1
+FLAG_OVERLAP_LAUNCH = 2      # the streaming kernel may start under the previous kernel's tail (see include/b2_w4a16.h)
+OVERLAP_LAUNCH = os.environ.get("B2_W4A16_OVERLAP", "1") != "0"
 
 
 def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None, flags=0):

@@ -156,6 +156,27 @@ StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     return p;
 }
 
+// Plain launch, or (dependent) a launch that may begin while the previous kernel of the stream is still
+// draining: its CTAs run up to their griddepcontrol.wait, which returns once that kernel has completed.
+template <typename Kernel, typename... Args>
+int launch_maybe_dependent(const char* name, Kernel kernel, int grid, int threads, int smem, cudaStream_t s, bool dependent,
+                           const Args&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(threads));
+    cfg.dynamicSmemBytes = size_t(smem);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+    if (e != cudaSuccess) return cuda_fail(name, e);
+    return B2_OK;
+}
+
 template <int MT, bool XVEC, int W, bool H16 = false>
 int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
     auto kernel = b2::w4a16_stream_kernel<MT, XVEC, W, H16>;
@@ -170,8 +191,7 @@ int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
-    kernel<<<grid, W * 32, smem, s>>>(a);
-    return after_launch("w4a16_stream_kernel");
+    return launch_maybe_dependent("w4a16_stream_kernel", kernel, grid, W * 32, smem, s, a.overlap != 0, a);
 }
 
 constexpr int kNotFused = -1000;            // internal: the fused projection + gather does not apply, use two launches
@@ -198,8 +218,7 @@ int launch_stream_gather_one(const b2::StreamArgs& a, const b2::GatherArgs& ga, 
         configured.fetch_or(bit, std::memory_order_release);
     }
     if ((long long)grid > (long long)per_sm[dev].load(std::memory_order_relaxed) * sms) return kNotFused;
-    kernel<<<grid, W * 32, smem, s>>>(a, ga);
-    return after_launch("w4a16_stream_gather_kernel");
+    return launch_maybe_dependent("w4a16_stream_gather_kernel", kernel, grid, W * 32, smem, s, a.overlap != 0, a, ga);
 }
 
 template <int MT, bool XVEC, int W>
@@ -369,7 +388,7 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
 int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t m,
                const b2::Dims& d, void* workspace, int64_t workspace_bytes, cudaStream_t s,
                const DeviceInfo& dev, const void* bias, int act = 0, bool h16 = false,
-               const b2::GatherArgs* ga = nullptr) {
+               const b2::GatherArgs* ga = nullptr, bool overlap = false) {
     const int64_t ticket_bytes = B2_W4A16_TICKET_BYTES;
     const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
     for (int64_t m0 = 0; m0 < m; m0 += B2_STREAM_MAX_M) {
@@ -393,6 +412,7 @@ int run_stream(const void* x, int64_t ldx, const void* native, void* y, int64_t 
         a.chunk_blocks = p.chunk_blocks; a.nchunks = p.nchunks;
         a.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
         a.fault_step = g_fault_step.exchange(-1, std::memory_order_relaxed);
+        a.overlap = overlap ? 1 : 0;
         int rc;
         if (ga) {
             // one launch for projection and gather: 16 rows at most, aligned x, the shipped 16- or 4-warp kernel
@@ -937,7 +957,7 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
-                          static_cast<cudaStream_t>(stream), dev, bias, act, h16, ga);
+                          static_cast<cudaStream_t>(stream), dev, bias, act, h16, ga, (flags & B2_FLAG_OVERLAP_LAUNCH) != 0);
     if (route == B2_ROUTE_TCGEN05) {
         if (!gemm_applicable(x, ldx, d))
             return fail(B2_ERR_UNSUPPORTED, "the tcgen05 route needs K % 8 == 0 and a 16-byte aligned x");
@@ -961,7 +981,7 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
 int b2_w4a16_linear_flags(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                           int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                           int64_t workspace_bytes, void* stream, int route, int flags) {
-    if (flags & ~B2_FLAG_FP16_STEPS) return fail(B2_ERR_ARGUMENT, "unknown flag");
+    if (flags & ~(B2_FLAG_FP16_STEPS | B2_FLAG_OVERLAP_LAUNCH)) return fail(B2_ERR_ARGUMENT, "unknown flag");
     return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, route, 0, flags);
 }
 
@@ -1111,7 +1131,7 @@ int b2_w4a16_linear_gather(const void* x, int64_t ldx, const void* native, const
                            void* const* flag_blocks, int64_t mailbox_slice_bytes, int rank, int world, int64_t m,
                            int64_t ld, int64_t n_total, int64_t slice_cols, int64_t k, void* workspace,
                            int64_t workspace_bytes, void* stream, int flags) {
-    if (flags & ~B2_FLAG_FP16_STEPS) return fail(B2_ERR_ARGUMENT, "unknown flag");
+    if (flags & ~(B2_FLAG_FP16_STEPS | B2_FLAG_OVERLAP_LAUNCH)) return fail(B2_ERR_ARGUMENT, "unknown flag");
     GatherCall c;
     if (int rc = make_gather_call(y_ranks, flag_blocks, mailbox_slice_bytes, rank, world, m, ld, n_total, slice_cols, c)) return rc;
     if (m == 0) return B2_OK;

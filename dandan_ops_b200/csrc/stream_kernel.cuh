@@ -97,6 +97,8 @@ struct StreamArgs {
     int wait_limit;         // mbarrier polls before a warp gives up (kWaitLimit; a test passes a small number)
     int fault_step;         // -1; a test passes n >= 0: warp 0 of CTA 0 arms the barrier of its n-th weight
                             // copy but does not issue the copy, so that the wait for it runs out
+    int overlap;            // launched as a programmatic dependent of the previous kernel: request weights first,
+                            // then wait for that kernel before anything else is read or written
 };
 
 // ---- small PTX helpers ------------------------------------------------------------------
@@ -443,7 +445,10 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
     const bool whole_x = a.kb <= kPhaseBlocks;
     uint8_t* xzero = xs + stream_x_bytes(W);
     if (threadIdx.x < kStreamZeroBytes / 16) reinterpret_cast<uint4*>(xzero)[threadIdx.x] = make_uint4(0, 0, 0, 0);
-    if (whole_x) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols, xrows, kChunk);
+    // Kernels launched behind this one as programmatic dependents may move onto SMs as they become free
+    // (no effect otherwise).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (whole_x && !a.overlap) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols, xrows, kChunk);
 
     // Copy-request cursor (used by lane 0): image block (fkb, 16*fgrp + warp).  Consecutive
     // column blocks of one row tile are `stride` bytes apart; at the end of a row group the
@@ -474,6 +479,12 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
             if (fetch < wb1) request(s);
     }
     __syncwarp();
+    if (a.overlap) {
+        // Weights are constant; everything else (x, bias, tickets, partial tiles, y) may belong to the previous
+        // kernel of the stream until it has completed and its writes are visible.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (whole_x) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols, xrows, kChunk);
+    }
 
     float acc[MT][4];
     int stage = 0;

@@ -227,11 +227,14 @@ class QuantizedLinear(torch.nn.Module):
     def _layer_flags(self):
         """Flags of the C ABI for this state.  FLAG_FP16_STEPS when every step is exactly representable in
         FP16 (checkpoints with FP16 scales): the decode kernels then use the FP16-only dequantization, which
-        is bit-identical for such steps.  Reads the steps once (a host sync), only when an image is (re)built -
+        is bit-identical for such steps; FLAG_OVERLAP_LAUNCH unless switched off (B2_W4A16_OVERLAP=0).  Reads the steps once (a host sync), only when an image is (re)built -
         never on the per-token path - and not while a stream is being captured."""
         if not self.scales.is_cuda or torch.cuda.is_current_stream_capturing():
             return 0
-        return _native.FLAG_FP16_STEPS if bool((self.scales.half().float() == self.scales).all()) else 0
+        flags = _native.FLAG_FP16_STEPS if bool((self.scales.half().float() == self.scales).all()) else 0
+        # The read above has synchronized the stream, so the image is complete in memory from here on: the
+        # decode kernel may start under the tail of whatever kernel precedes it (FLAG_OVERLAP_LAUNCH).
+        return flags | (_native.FLAG_OVERLAP_LAUNCH if _native.OVERLAP_LAUNCH else 0)
 
     def attach_native_image(self, image):
         """Use a prebuilt device image of THIS layer's state (e.g. from `checkpoint.ImageCache`)

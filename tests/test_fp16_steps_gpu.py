@@ -24,14 +24,15 @@ def _direct_layer(n, k, seed):
 
 
 def test_module_sets_the_flag_only_for_fp16_representable_steps():
-    assert _direct_layer(100, 300, 1)._image_flags == _native.FLAG_FP16_STEPS
+    fp16 = _native.FLAG_FP16_STEPS
+    assert _direct_layer(100, 300, 1)._image_flags & fp16
     g = torch.Generator().manual_seed(2)
     quantized = ops.QuantizedLinear.from_float((torch.randn(64, 256, generator=g) * 0.02).half().cuda())
-    assert quantized._image_flags == 0                       # hi/15 - lo/15 is an FP32 number
+    assert not quantized._image_flags & fp16                 # hi/15 - lo/15 is an FP32 number
     layer = _direct_layer(100, 300, 3)
     layer.scales.mul_(1.0001)                                # steps change: the image and its flags are rebuilt
     layer._native_image()
-    assert layer._image_flags == 0
+    assert not layer._image_flags & fp16
 
 
 @pytest.mark.parametrize("route", [_native.ROUTE_TILE, _native.ROUTE_STREAM])
@@ -47,7 +48,7 @@ def test_fp16_step_chain_is_bit_identical_to_the_general_chain(route, m, n, k):
     general = guarded_linear(x, image, n, k, route=route)
     fast = _native.linear(x, image, n, k, route=route, flags=_native.FLAG_FP16_STEPS)
     assert torch.equal(fast, general)
-    assert lib.b2_w4a16_linear_flags(x.data_ptr(), k, image.data_ptr(), None, fast.data_ptr(), n, m, n, k, None, 0, None, route, 2) != 0
+    assert lib.b2_w4a16_linear_flags(x.data_ptr(), k, image.data_ptr(), None, fast.data_ptr(), n, m, n, k, None, 0, None, route, 8) != 0
     assert b"unknown flag" in lib.b2_w4a16_last_error()
 
 

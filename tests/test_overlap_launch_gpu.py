@@ -1,0 +1,84 @@
+"""B2_FLAG_OVERLAP_LAUNCH: the streaming kernel launched as a programmatic dependent of the previous kernel
+of the stream.  Its CTAs may start while that kernel drains, but they read x, bias and the workspace only after
+it has completed - so a chain in which every call consumes the previous call's output must give the same bits
+with and without the flag, eagerly and replayed from a CUDA graph."""
+import pytest
+import torch
+
+from dandan_ops_b200 import _native
+from dandan_ops_b200.quantized_linear import QuantizedLinear
+
+pytestmark = pytest.mark.gpu
+STREAM = _native.ROUTE_STREAM
+
+
+def _layers(n, k, count, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [QuantizedLinear.from_float((torch.randn(n, k, generator=g) * 0.02).cuda(), torch.randn(n, generator=g).cuda())
+            for _ in range(count)]
+
+
+def _chain(layers, x, flags, outs):
+    """x -> layer 0 -> layer 1 -> ...: every call's x is the previous call's y (square layers)."""
+    cur = x
+    for layer, out in zip(layers, outs):
+        _native.linear(cur, layer._native_image(), layer.out_features, layer.in_features, route=STREAM, out=out,
+                       bias=layer._bias_fp16(), flags=flags)
+        cur = out
+    return cur
+
+
+@pytest.mark.parametrize("m", [1, 8, 16, 40])
+@pytest.mark.parametrize("n", [2048, 4096])
+def test_dependent_chain_matches_the_serial_chain(m, n):
+    layers = _layers(n, n, 6, 100 + m + n)
+    x = torch.randn(m, n, generator=torch.Generator().manual_seed(m)).half().cuda()
+    plain = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
+    over = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
+    _chain(layers, x, 0, plain)
+    for _ in range(3):
+        for t in over:
+            t.fill_(float("nan"))
+        _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over)
+        torch.cuda.synchronize()
+        for a, b in zip(plain, over):
+            assert torch.equal(a, b)
+    assert _native.status() == 0
+
+
+def test_graph_replay_of_a_dependent_chain():
+    m, n = 8, 4096
+    layers = _layers(n, n, 5, 7)
+    x = torch.randn(m, n, generator=torch.Generator().manual_seed(3)).half().cuda()
+    plain = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
+    over = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
+    _chain(layers, x, 0, plain)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with _native.private_workspace(), torch.cuda.graph(graph, stream=stream):
+            _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over)
+        for _ in range(4):
+            for t in over:
+                t.fill_(float("nan"))
+            graph.replay()
+            stream.synchronize()
+            for a, b in zip(plain, over):
+                assert torch.equal(a, b)
+
+
+def test_module_forward_uses_the_flag_and_other_routes_ignore_it():
+    assert _native.OVERLAP_LAUNCH
+    layer = _layers(1024, 1024, 1, 5)[0]
+    assert layer._image_flags & _native.FLAG_OVERLAP_LAUNCH
+    x = torch.randn(4, 1024, generator=torch.Generator().manual_seed(1)).half().cuda()
+    for route in (_native.ROUTE_TILE, _native.ROUTE_STREAM, _native.ROUTE_AUTO):
+        want = _native.linear(x, layer._native_image(), 1024, 1024, route=route, bias=layer._bias_fp16())
+        got = _native.linear(x, layer._native_image(), 1024, 1024, route=route, bias=layer._bias_fp16(),
+                             flags=_native.FLAG_OVERLAP_LAUNCH)
+        assert torch.equal(got, want)
+    assert torch.equal(layer(x), want)
+    with pytest.raises(RuntimeError, match="unknown flag"):
+        _native.linear(x, layer._native_image(), 1024, 1024, flags=4)
