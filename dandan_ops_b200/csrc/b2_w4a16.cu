@@ -321,7 +321,7 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
         if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
         configured.fetch_or(bit, std::memory_order_release);
     }
-    if (a.ksplit == 1) {
+    if (a.ksplit == 1 && !a.overlap) {
         kernel<<<a.n16, a.warps * 32, smem, s>>>(a);
         return after_launch("w4a16_tile_kernel");
     }
@@ -330,11 +330,20 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
     cfg.blockDim = dim3(unsigned(a.warps) * 32, 1, 1);
     cfg.dynamicSmemBytes = size_t(smem);
     cfg.stream = s;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = unsigned(a.ksplit); attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute attr[2];
+    int count = 0;
+    if (a.ksplit > 1) {
+        attr[count].id = cudaLaunchAttributeClusterDimension;
+        attr[count].val.clusterDim.x = unsigned(a.ksplit); attr[count].val.clusterDim.y = 1; attr[count].val.clusterDim.z = 1;
+        ++count;
+    }
+    if (a.overlap) {          // may start under the previous kernel's tail, see B2_FLAG_OVERLAP_LAUNCH
+        attr[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = unsigned(count);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, a);
     if (le != cudaSuccess) return cuda_fail("w4a16_tile_kernel", le);
@@ -343,9 +352,10 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
 
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
              const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0, int sms = 148,
-             bool h16 = false) {
+             bool h16 = false, bool overlap = false) {
     b2::TileArgs a;
     a.act = act;
+    a.overlap = overlap ? 1 : 0;
     a.x = static_cast<const __half*>(x);
     a.native = static_cast<const uint8_t*>(native);
     a.y = static_cast<__half*>(y);
@@ -953,7 +963,8 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
         if (!tile_applicable(m, d, tile_split))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
-        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count, h16);
+        return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count, h16,
+                        (flags & B2_FLAG_OVERLAP_LAUNCH) != 0);
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,

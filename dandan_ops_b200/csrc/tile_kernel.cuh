@@ -41,6 +41,8 @@ struct TileArgs {
     int ksplit;             // 1, 2 or 4: a cluster of that many CTAs shares a row tile, each takes its share
                             // of the K blocks and the others hand their 16 x 8*MT sums to the first through
                             // distributed shared memory (layers whose row tiles leave most SMs idle)
+    int overlap;            // launched as a programmatic dependent of the previous kernel: all weight copies are
+                            // requested first, then the kernel waits for that one before it reads x
 };
 
 // `rows` = rows of x that exist (1..16): only those are staged, so that at M = 1 a CTA of a
@@ -94,6 +96,10 @@ w4a16_tile_kernel(const TileArgs a) {
                 bulk_copy_g2s(smem_u32(blocks + b * kBlockBytes), src + b * stride, kBlockBytes, bar0 + b * 8);
         }
     }
+    // Kernels launched behind this one as programmatic dependents may start as soon as they find room.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // The weights are constant; x, the bias and y may belong to the previous kernel until it has completed.
+    if (a.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
     // stage x for all columns (zero beyond M and K)
     {
         // Copies that bypass registers (cp.async) are the faster form for the small grids of a K split

@@ -166,13 +166,14 @@ int b2_w4a16_linear_bias(const void* x, int64_t ldx, const void* native, const v
  * set on a layer with other steps it gives wrong weights.  No counterpart in the reference (its kernels
  * multiply in FP32 throughout, kernels/w4a16_small.cuh:39). */
 #define B2_FLAG_FP16_STEPS 1
-/* B2_FLAG_OVERLAP_LAUNCH: the streaming decode kernel may start before the previous kernel of the stream has
- * finished (programmatic dependent launch).  As SMs of the previous kernel drain, CTAs of this one move in,
- * set up their barriers and request their first weight blocks; they touch x, bias, y and the workspace only
- * after the previous kernel has completed and its writes are visible (griddepcontrol.wait).  The caller
- * asserts that the weight IMAGE is not being written by work still in flight on the stream (it is constant
- * after the layer was built).  Hides the launch latency and the first trip of the weights behind the previous
- * kernel's tail; results are unchanged.  Routes other than the streaming kernel ignore the flag. */
+/* B2_FLAG_OVERLAP_LAUNCH: the decode kernels (tile and streaming) may start before the previous kernel of the
+ * stream has finished (programmatic dependent launch).  As that kernel drains, CTAs of this one move in, set
+ * up their barriers and request their weight blocks (the tile kernel all of them, the streaming kernel the
+ * first ring); they touch x, bias, y and the workspace only after the previous kernel has completed and its
+ * writes are visible (griddepcontrol.wait).  The caller asserts that the weight IMAGE is not being written by
+ * work still in flight on the stream (it is constant after the layer was built).  Hides the launch latency and
+ * the first trip of the weights behind the previous kernel's tail; results are unchanged.  The tensor-core
+ * GEMM ignores the flag. */
 #define B2_FLAG_OVERLAP_LAUNCH 2
 int b2_w4a16_linear_flags(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                           int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,

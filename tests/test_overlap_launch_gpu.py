@@ -1,4 +1,4 @@
-"""B2_FLAG_OVERLAP_LAUNCH: the streaming kernel launched as a programmatic dependent of the previous kernel
+"""B2_FLAG_OVERLAP_LAUNCH: the decode kernels launched as programmatic dependents of the previous kernel
 of the stream.  Its CTAs may start while that kernel drains, but they read x, bias and the workspace only after
 it has completed - so a chain in which every call consumes the previous call's output must give the same bits
 with and without the flag, eagerly and replayed from a CUDA graph."""
@@ -18,48 +18,52 @@ def _layers(n, k, count, seed):
             for _ in range(count)]
 
 
-def _chain(layers, x, flags, outs):
+def _chain(layers, x, flags, outs, route=STREAM):
     """x -> layer 0 -> layer 1 -> ...: every call's x is the previous call's y (square layers)."""
     cur = x
     for layer, out in zip(layers, outs):
-        _native.linear(cur, layer._native_image(), layer.out_features, layer.in_features, route=STREAM, out=out,
+        _native.linear(cur, layer._native_image(), layer.out_features, layer.in_features, route=route, out=out,
                        bias=layer._bias_fp16(), flags=flags)
         cur = out
     return cur
 
 
+@pytest.mark.parametrize("route", [STREAM, _native.ROUTE_TILE, _native.ROUTE_AUTO])
 @pytest.mark.parametrize("m", [1, 8, 16, 40])
-@pytest.mark.parametrize("n", [2048, 4096])
-def test_dependent_chain_matches_the_serial_chain(m, n):
+@pytest.mark.parametrize("n", [1024, 2048, 4096])
+def test_dependent_chain_matches_the_serial_chain(m, n, route):
+    if route == _native.ROUTE_TILE and m > 16:
+        pytest.skip("the tile route takes at most 16 rows")
     layers = _layers(n, n, 6, 100 + m + n)
     x = torch.randn(m, n, generator=torch.Generator().manual_seed(m)).half().cuda()
     plain = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
     over = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
-    _chain(layers, x, 0, plain)
+    _chain(layers, x, 0, plain, route)
     for _ in range(3):
         for t in over:
             t.fill_(float("nan"))
-        _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over)
+        _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over, route)
         torch.cuda.synchronize()
         for a, b in zip(plain, over):
             assert torch.equal(a, b)
     assert _native.status() == 0
 
 
-def test_graph_replay_of_a_dependent_chain():
-    m, n = 8, 4096
+@pytest.mark.parametrize("route,n", [(STREAM, 4096), (_native.ROUTE_TILE, 1024)])
+def test_graph_replay_of_a_dependent_chain(route, n):
+    m = 8
     layers = _layers(n, n, 5, 7)
     x = torch.randn(m, n, generator=torch.Generator().manual_seed(3)).half().cuda()
     plain = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
     over = [torch.empty(m, n, dtype=torch.float16, device="cuda") for _ in layers]
-    _chain(layers, x, 0, plain)
+    _chain(layers, x, 0, plain, route)
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
-        _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over)
+        _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over, route)
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with _native.private_workspace(), torch.cuda.graph(graph, stream=stream):
-            _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over)
+            _chain(layers, x, _native.FLAG_OVERLAP_LAUNCH, over, route)
         for _ in range(4):
             for t in over:
                 t.fill_(float("nan"))
@@ -69,7 +73,7 @@ def test_graph_replay_of_a_dependent_chain():
                 assert torch.equal(a, b)
 
 
-def test_module_forward_uses_the_flag_and_other_routes_ignore_it():
+def test_module_forward_uses_the_flag_on_every_route():
     assert _native.OVERLAP_LAUNCH
     layer = _layers(1024, 1024, 1, 5)[0]
     assert layer._image_flags & _native.FLAG_OVERLAP_LAUNCH
