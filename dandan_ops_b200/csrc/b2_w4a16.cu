@@ -878,6 +878,8 @@ residual_rms_norm_kernel(const __half* x, int64_t ldx, const __half* residual, i
                          const __half* weight, float eps, __half* summed, int64_t lds,
                          __half* out, int64_t ldo, int m, int k) {
     __shared__ b2::NormScratch scratch;
+    // a projection launched behind this kernel as a programmatic dependent may fetch its weights meanwhile
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int row = blockIdx.x;
     __half* o = out + row * ldo;
     b2::norm_row(x + row * ldx, residual ? residual + row * ldr : nullptr, weight, eps, summed ? summed + row * lds : o, o, k, scratch);
@@ -1030,7 +1032,11 @@ int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, in
         static_cast<const __half*>(norm_weight), eps, static_cast<__half*>(summed), lds,
         static_cast<__half*>(xn_scratch), k, int(m), int(k));
     if (int rc = after_launch("residual_rms_norm_kernel")) return rc;
-    return linear_impl(xn_scratch, k, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 0);
+    // The projection starts under the norm kernel (its weight copies do not depend on it) and reads xn_scratch
+    // after that kernel has completed.  The norm kernel itself is an ordinary launch, so everything issued
+    // before this call - including whatever wrote the weight image - has finished before either kernel runs.
+    return linear_impl(xn_scratch, k, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 0,
+                       B2_FLAG_OVERLAP_LAUNCH);
 }
 
 int b2_w4a16_residual_rms_norm(const void* x, int64_t ldx, const void* residual, int64_t ldr, const void* norm_weight,
