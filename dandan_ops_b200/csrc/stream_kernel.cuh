@@ -411,13 +411,13 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
     constexpr int kWarps = W;
     constexpr int kBarBytes = stream_bar_bytes(W), kRingBytes = stream_ring_bytes(W);
     // Up to 8 rows of x only the rows that exist are staged (rows beyond M are zero B fragments, read from a
-    // 128-byte row of zeros): at M = 1 the x buffer then holds 118 column blocks instead of 16, so x is
-    // staged once per CTA for every K up to 30 000 and the CTA never stops for an x phase again.
+    // 128-byte row of zeros): at M = 1 the x buffer of a 16-warp CTA then holds 244 column blocks instead of
+    // 33, so x is staged once per CTA for every K up to 62 000 and the CTA never stops for an x phase again.
     const int xrows = MT == 1 ? a.m : MP;
     // rows of 144 bytes, padded so that consecutive chunks sit 32 bytes apart modulo 128: the eight lanes of a
     // quarter warp (two rows, four chunks) then read eight different 16-byte bank groups for any row count
     const int kChunk = xrows * 144 + ((32 - xrows * 16) & 127);
-    const int kPhaseBlocks = stream_x_bytes(W) / (4 * kChunk);      // W=16, all rows staged: 16, 8, 4, 2 column blocks
+    const int kPhaseBlocks = stream_x_bytes(W) / (4 * kChunk);      // W=16, all rows staged: 33, 16, 8, 4 column blocks
     static_assert(stream_x_bytes(W) / (4 * stream_x_chunk_bytes(MP)) >= 1, "x phase must hold at least one column block");
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
