@@ -152,21 +152,35 @@ __device__ __forceinline__ bool mailbox_receive(const GatherArgs& a, unsigned ep
         const int64_t cols = max(int64_t(0), min(a.slice_cols, a.n_total - col0));
         const int64_t wpr = cols >> 1, words = int64_t(a.m) * wpr;
         const uint2* box = mailbox(mine, a.world, a.slots, parity, q);
-        for (int64_t s = first; s < words; s += stride) {
-            unsigned data = 0, tag = 0;
-            unsigned long long t0 = 0;
-            for (long long i = 0; i < a.wait_ns / 64 + 4096; ++i) {        // bounded by the clock and by the count
-                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data), "=r"(tag) : "l"(box + s) : "memory");
-                if (tag == epoch || gave_up) break;
-                if (i == 4096) t0 = global_ns();
-                if (i > 4096) {
-                    if (global_ns() - t0 > (unsigned long long)a.wait_ns) { gave_up = true; break; }
-                    __nanosleep(100);
-                }
+        // Four packets per thread are requested at once (the loads are independent); a packet that has not
+        // arrived yet is then polled on its own.
+        for (int64_t s0 = first; s0 < words; s0 += 4 * stride) {
+            unsigned data[4], tag[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int64_t s = s0 + j * stride;
+                data[j] = 0;
+                tag[j] = epoch - 1u;
+                if (s < words)
+                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data[j]), "=r"(tag[j]) : "l"(box + s) : "memory");
             }
-            if (tag != epoch) { gave_up = true; continue; }
-            const int64_t row = s / wpr, w = s - row * wpr;
-            *reinterpret_cast<unsigned*>(y + row * a.ld + col0 + 2 * w) = data;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int64_t s = s0 + j * stride;
+                if (s >= words) break;
+                unsigned long long t0 = 0;
+                for (long long i = 0; tag[j] != epoch && !gave_up && i < a.wait_ns / 64 + 4096; ++i) {   // bounded by the clock and by the count
+                    if (i == 4096) t0 = global_ns();
+                    if (i > 4096) {
+                        if (global_ns() - t0 > (unsigned long long)a.wait_ns) { gave_up = true; break; }
+                        __nanosleep(100);
+                    }
+                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data[j]), "=r"(tag[j]) : "l"(box + s) : "memory");
+                }
+                if (tag[j] != epoch) { gave_up = true; continue; }
+                const int64_t row = s / wpr, w = s - row * wpr;
+                *reinterpret_cast<unsigned*>(y + row * a.ld + col0 + 2 * w) = data[j];
+            }
         }
     }
     return gave_up;
