@@ -50,6 +50,7 @@ _SIGNATURES = {
     "b2_w4a16_linear_bias": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_linear_flags": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int, _int]),
     "b2_w4a16_linear_silu_mul": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "b2_w4a16_linear_silu_mul_flags": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp, _int]),
     "b2_w4a16_silu_mul_is_fused": (_int, [_i64, _i64, _i64]),
     "b2_w4a16_silu_mul_pairs": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b2_w4a16_rmsnorm_linear": (_int, [_vp, _i64, _vp, _i64, _vp, ctypes.c_float, _vp, _i64, _vp, _vp, _vp, _vp, _i64,
@@ -371,7 +372,7 @@ def linear(x, image, n, k, route=ROUTE_AUTO, out=None, bias=None, flags=0):
     return y
 
 
-def linear_silu_mul(x, image, n, k, bias=None, out=None):
+def linear_silu_mul(x, image, n, k, bias=None, out=None, flags=0):
     """Fused gate/up projection on a pair-ordered image: [M, K] -> [M, N/2] (see include/b2_w4a16.h).
     The epilogue runs inside the decode kernels and the pair GEMM; the few problems that take a
     single-CTA GEMM tile run the projection and then the elementwise pair kernel."""
@@ -385,13 +386,13 @@ def linear_silu_mul(x, image, n, k, bias=None, out=None):
         stream = _stream()
         aligned = x.data_ptr() % 16 == 0 and (m == 1 or x.stride(0) % 8 == 0)
         if not lib.b2_w4a16_silu_mul_is_fused(m, n, k) or (m > STREAM_MAX_M and not aligned and k % 8 == 0):
-            full = linear(x, image, n, k, bias=bias)
+            full = linear(x, image, n, k, bias=bias, flags=flags)
             _check(lib.b2_w4a16_silu_mul_pairs(full.data_ptr(), full.stride(0), y.data_ptr(), y.stride(0), m, n, stream))
             return y
         ws = workspace(device, int(lib.b2_w4a16_workspace_bytes(m, n, k)))
-        _check(lib.b2_w4a16_linear_silu_mul(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
-                                            bias.data_ptr() if bias is not None else None, y.data_ptr(),
-                                            y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream))
+        _check(lib.b2_w4a16_linear_silu_mul_flags(x.data_ptr(), x.stride(0) if m > 1 else k, image.data_ptr(),
+                                                  bias.data_ptr() if bias is not None else None, y.data_ptr(),
+                                                  y.stride(0), m, n, k, ws.data_ptr(), ws.numel(), stream, flags))
     return y
 
 

@@ -1004,6 +1004,13 @@ int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, con
     return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 1);
 }
 
+int b2_w4a16_linear_silu_mul_flags(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                                   int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                                   int64_t workspace_bytes, void* stream, int flags) {
+    if (flags & ~(B2_FLAG_FP16_STEPS | B2_FLAG_OVERLAP_LAUNCH)) return fail(B2_ERR_ARGUMENT, "unknown flag");
+    return linear_impl(x, ldx, native, bias_fp16, y, ldy, m, n, k, workspace, workspace_bytes, stream, B2_ROUTE_AUTO, 1, flags);
+}
+
 int b2_w4a16_rmsnorm_linear(const void* x, int64_t ldx, const void* residual, int64_t ldr, const void* norm_weight,
                             float eps, void* summed, int64_t lds, void* xn_scratch, const void* native,
                             const void* bias_fp16, void* y, int64_t ldy, int64_t m, int64_t n, int64_t k,

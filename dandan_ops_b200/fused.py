@@ -122,8 +122,9 @@ class GateUpSilu(nn.Module):
             raise ValueError("the fused gate/up projection requires CUDA FP16 input on the layer's device")
         if x.stride(1) != 1:
             x = x.contiguous()
-        return _native.linear_silu_mul(x, self.op._native_image(), self.op.out_features, self.in_features,
-                                       bias=self.op._bias_fp16())
+        image = self.op._native_image()
+        return _native.linear_silu_mul(x, image, self.op.out_features, self.in_features, bias=self.op._bias_fp16(),
+                                       flags=self.op._image_flags & _native.FLAG_OVERLAP_LAUNCH)
 
     def unfuse(self):
         """The original (gate, up) layers, state bit-identical."""

@@ -193,6 +193,10 @@ int b2_w4a16_linear_flags(const void* x, int64_t ldx, const void* native, const 
 int b2_w4a16_linear_silu_mul(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
                              int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
                              int64_t workspace_bytes, void* stream);
+/* Same with the layer flags of b2_w4a16_linear_flags (FP16-step dequantization, overlap launch). */
+int b2_w4a16_linear_silu_mul_flags(const void* x, int64_t ldx, const void* native, const void* bias_fp16, void* y,
+                                   int64_t ldy, int64_t m, int64_t n, int64_t k, void* workspace,
+                                   int64_t workspace_bytes, void* stream, int flags);
 int b2_w4a16_silu_mul_is_fused(int64_t m, int64_t n, int64_t k);
 
 /* Residual add + RMSNorm in front of a projection (the step before the qkv projection of a decoder

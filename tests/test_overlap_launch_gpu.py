@@ -86,3 +86,25 @@ def test_module_forward_uses_the_flag_on_every_route():
     assert torch.equal(layer(x), want)
     with pytest.raises(RuntimeError, match="unknown flag"):
         _native.linear(x, layer._native_image(), 1024, 1024, flags=4)
+
+
+@pytest.mark.parametrize("m", [1, 8, 40])
+def test_fused_gate_up_behind_a_producer_kernel(m):
+    """x of the fused gate/up call is written by the call before it; with the flag the result must not change."""
+    from dandan_ops_b200.fused import GateUpSilu
+    k, inter = 2048, 4096
+    g = torch.Generator().manual_seed(17 + m)
+    producer = _layers(k, k, 1, 3)[0]
+    gate, up = (QuantizedLinear.from_float((torch.randn(inter, k, generator=g) * 0.02).cuda()) for _ in range(2))
+    fused = GateUpSilu(gate, up)
+    x0 = torch.randn(m, k, generator=g).half().cuda()
+    mid = torch.empty(m, k, dtype=torch.float16, device="cuda")
+    results = []
+    for flags in (0, _native.FLAG_OVERLAP_LAUNCH, _native.FLAG_OVERLAP_LAUNCH):
+        mid.fill_(float("nan"))
+        _native.linear(x0, producer._native_image(), k, k, out=mid, bias=producer._bias_fp16(), flags=flags)
+        results.append(_native.linear_silu_mul(mid, fused.op._native_image(), fused.op.out_features, k,
+                                               bias=fused.op._bias_fp16(), flags=flags).clone())
+    torch.cuda.synchronize()
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
+    assert torch.equal(fused(mid), results[0])
