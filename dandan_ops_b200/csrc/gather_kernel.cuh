@@ -146,41 +146,48 @@ __device__ __forceinline__ bool mailbox_receive(const GatherArgs& a, unsigned ep
     __half* y = a.y[a.rank];
     const unsigned parity = epoch & 1u;
     bool gave_up = false;
-    for (int q = 0; q < a.world; ++q) {
-        if (q == a.rank) continue;
-        const int64_t col0 = int64_t(q) * a.slice_cols;
-        const int64_t cols = max(int64_t(0), min(a.slice_cols, a.n_total - col0));
-        const int64_t wpr = cols >> 1, words = int64_t(a.m) * wpr;
-        const uint2* box = mailbox(mine, a.world, a.slots, parity, q);
-        // Four packets per thread are requested at once (the loads are independent); a packet that has not
-        // arrived yet is then polled on its own.
-        for (int64_t s0 = first; s0 < words; s0 += 4 * stride) {
-            unsigned data[4], tag[4];
+    // One index space over all peers (a full slice has `full` words; the last rank's may be shorter), so that a
+    // thread's packets from different peers are requested together: four loads in flight per thread, one trip
+    // to L2 for the common case instead of one per peer.
+    const int64_t full = int64_t(a.m) * (a.slice_cols >> 1);
+    const int64_t total = full * (a.world - 1);
+    for (int64_t i0 = first; i0 < total; i0 += 4 * stride) {
+        unsigned data[4], tag[4];
+        const uint2* slot[4];
+        unsigned* dst[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int64_t s = s0 + j * stride;
-                data[j] = 0;
-                tag[j] = epoch - 1u;
-                if (s < words)
-                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data[j]), "=r"(tag[j]) : "l"(box + s) : "memory");
-            }
+        for (int j = 0; j < 4; ++j) {
+            const int64_t i = i0 + j * stride;
+            slot[j] = nullptr;
+            dst[j] = nullptr;
+            data[j] = 0;
+            tag[j] = epoch;
+            if (i >= total) continue;
+            const int pi = int(i / full);
+            const int q = pi < a.rank ? pi : pi + 1;
+            const int64_t s = i - pi * full;
+            const int64_t col0 = int64_t(q) * a.slice_cols;
+            const int64_t wpr = max(int64_t(0), min(a.slice_cols, a.n_total - col0)) >> 1;
+            if (s >= int64_t(a.m) * wpr) continue;                         // beyond a short last slice
+            const int64_t row = s / wpr, w = s - row * wpr;
+            slot[j] = mailbox(mine, a.world, a.slots, parity, q) + s;
+            dst[j] = reinterpret_cast<unsigned*>(y + row * a.ld + col0 + 2 * w);
+            asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data[j]), "=r"(tag[j]) : "l"(slot[j]) : "memory");
+        }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int64_t s = s0 + j * stride;
-                if (s >= words) break;
-                unsigned long long t0 = 0;
-                for (long long i = 0; tag[j] != epoch && !gave_up && i < a.wait_ns / 64 + 4096; ++i) {   // bounded by the clock and by the count
-                    if (i == 4096) t0 = global_ns();
-                    if (i > 4096) {
-                        if (global_ns() - t0 > (unsigned long long)a.wait_ns) { gave_up = true; break; }
-                        __nanosleep(100);
-                    }
-                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data[j]), "=r"(tag[j]) : "l"(box + s) : "memory");
+        for (int j = 0; j < 4; ++j) {
+            if (!slot[j]) continue;
+            unsigned long long t0 = 0;
+            for (long long n = 0; tag[j] != epoch && !gave_up && n < a.wait_ns / 64 + 4096; ++n) {   // bounded by the clock and by the count
+                if (n == 4096) t0 = global_ns();
+                if (n > 4096) {
+                    if (global_ns() - t0 > (unsigned long long)a.wait_ns) { gave_up = true; break; }
+                    __nanosleep(100);
                 }
-                if (tag[j] != epoch) { gave_up = true; continue; }
-                const int64_t row = s / wpr, w = s - row * wpr;
-                *reinterpret_cast<unsigned*>(y + row * a.ld + col0 + 2 * w) = data[j];
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data[j]), "=r"(tag[j]) : "l"(slot[j]) : "memory");
             }
+            if (tag[j] != epoch) { gave_up = true; continue; }
+            *dst[j] = data[j];
         }
     }
     return gave_up;
