@@ -29,7 +29,8 @@ QuantizedLinear.from_float(group_size=64), x ~ N(0,1) FP16):
 (the last two run one replica per rank at N > 1: weak scaling, no exchange)
 
 `--impl reference` times the reference's own CPU route on the host cores: the reference package when
-it can be imported (B2_REFERENCE_ROOT or /root/reference), else the oracle's restatement of it.
+it can be imported (a checkout named by the environment variable B2_REFERENCE_ROOT), else the oracle's
+restatement of it.
 """
 import argparse
 import copy
@@ -665,8 +666,8 @@ def warm_protocol(stream, device):
 # CPU baseline / reference arm: the reference's CPU route on the host cores
 # ----------------------------------------------------------------------------------------------
 def import_reference():
-    """The reference package, if a checkout is reachable (B2_REFERENCE_ROOT or /root/reference); else None."""
-    for root in (os.environ.get("B2_REFERENCE_ROOT"), "/root/reference"):
+    """The reference package, if the environment variable B2_REFERENCE_ROOT names a checkout of it; else None."""
+    for root in (os.environ.get("B2_REFERENCE_ROOT"),):
         if root and (Path(root) / "dandan_ops" / "quantized_linear.py").is_file():
             sys.path.insert(0, root)
             try:
