@@ -140,7 +140,7 @@ StreamPlan plan_stream(int64_t m, const b2::Dims& d, int sm_count) {
     // ticket and nchunks or a few more partial slots.
     p.chunk_blocks = 0;
     p.nchunks = 1;
-    const int xblocks = stream_x_blocks(16, p.mt == 1 ? p.rows : p.mt * 8);
+    const int xblocks = stream_x_blocks(16, (p.mt == 1 && p.rows <= 4) ? p.rows : p.mt * 8);
     // Measured 2-8 % behind the one-dimensional split on the 8B/70B projections (the fence + ticket round trip of
     // every tile costs more than the x phases it removes), so it runs only when asked for (stream_variant 4).
     if (p.warps == 16 && p.mt <= 2 && variant == 4 && d.kb > xblocks && p.grid > 1) {
@@ -177,9 +177,15 @@ int launch_maybe_dependent(const char* name, Kernel kernel, int grid, int thread
     return B2_OK;
 }
 
-template <int MT, bool XVEC, int W, bool H16 = false>
+// Up to this many rows of x the streaming kernel stages only the rows that exist (template parameter XROWS).
+constexpr int kStreamExactRows = 4;
+
+template <int MT, bool XVEC, int W, bool H16 = false, bool XROWS = false>
 int launch_stream_one(const b2::StreamArgs& a, int grid, cudaStream_t s) {
-    auto kernel = b2::w4a16_stream_kernel<MT, XVEC, W, H16>;
+    if constexpr (MT == 1 && !XROWS) {
+        if (a.m <= kStreamExactRows) return launch_stream_one<MT, XVEC, W, H16, true>(a, grid, s);
+    }
+    auto kernel = b2::w4a16_stream_kernel<MT, XVEC, W, H16, XROWS>;
     constexpr int smem = b2::stream_smem_bytes(W);
     // Opt in to >48 KB of dynamic shared memory once per device and instantiation.
     static std::atomic<uint64_t> configured{0};
@@ -198,9 +204,12 @@ constexpr int kNotFused = -1000;            // internal: the fused projection + 
 
 // Projection + all-gather in one launch (w4a16_stream_gather_kernel).  Its CTAs wait for packets from other
 // GPUs, so the whole grid must be resident at once: checked against the occupancy the runtime reports.
-template <int MT, int W, bool H16>
+template <int MT, int W, bool H16, bool XROWS = false>
 int launch_stream_gather_one(const b2::StreamArgs& a, const b2::GatherArgs& ga, int grid, int sms, cudaStream_t s) {
-    auto kernel = b2::w4a16_stream_gather_kernel<MT, W, H16>;
+    if constexpr (MT == 1 && !XROWS) {
+        if (a.m <= kStreamExactRows) return launch_stream_gather_one<MT, W, H16, true>(a, ga, grid, sms, s);
+    }
+    auto kernel = b2::w4a16_stream_gather_kernel<MT, W, H16, XROWS>;
     constexpr int smem = b2::stream_smem_bytes(W);
     static std::atomic<uint64_t> configured{0};
     static std::atomic<int> per_sm[64];

@@ -96,7 +96,8 @@ struct StreamArgs {
     int nchunks;            //   and the number of chunks (0 / 1 in the other kernels)
     int wait_limit;         // mbarrier polls before a warp gives up (kWaitLimit; a test passes a small number)
     int fault_step;         // -1; a test passes n >= 0: warp 0 of CTA 0 arms the barrier of its n-th weight
-                            // copy but does not issue the copy, so that the wait for it runs out
+                            // copy but does not issue the copy, so that the wait for it runs out (only the copies
+                            // of the first ring fill, n < B2_STREAM_STAGES, are looked at)
     int overlap;            // launched as a programmatic dependent of the previous kernel: request weights first,
                             // then wait for that kernel before anything else is read or written
 };
@@ -333,7 +334,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: false if the phase did not complete within kWaitLimit polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = kWaitLimit) {
-    for (int i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;           // the common case costs no loop bookkeeping
+    for (int i = 1; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
@@ -404,7 +406,10 @@ __device__ __forceinline__ int owner_of(int s, int steps, int ctas) {
 // peer's memory; every wait is bounded (status bit 2 of the flag block on a timeout).  A CTA waits only for
 // packets of OTHER GPUs, whose senders never wait before they send, so the launch needs no co-residency
 // with anything but its own grid (the host checks that the whole grid fits on the device at once).
-template <int MT, bool XVEC, int W, bool H16, bool GATHER>
+// XROWS (MT = 1 only): stage just the rows of x that exist.  The row count is then a run-time number in the
+// x addressing of every block (measured: 28 more instructions per block at M = 8, 13 fewer at M = 1, where most
+// lanes read the zero row), so batches of 5 to 8 rows use the compile-time layout of all 8 rows instead.
+template <int MT, bool XVEC, int W, bool H16, bool GATHER, bool XROWS>
 __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArgs* ga) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MP = MT * 8;
@@ -413,7 +418,7 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
     // Up to 8 rows of x only the rows that exist are staged (rows beyond M are zero B fragments, read from a
     // 128-byte row of zeros): at M = 1 the x buffer of a 16-warp CTA then holds 244 column blocks instead of
     // 33, so x is staged once per CTA for every K up to 62 000 and the CTA never stops for an x phase again.
-    const int xrows = MT == 1 ? a.m : MP;
+    const int xrows = (MT == 1 && XROWS) ? a.m : MP;
     // rows of 144 bytes, padded so that consecutive chunks sit 32 bytes apart modulo 128: the eight lanes of a
     // quarter warp (two rows, four chunks) then read eight different 16-byte bank groups for any row count
     const int kChunk = xrows * 144 + ((32 - xrows * 16) & 127);
@@ -458,10 +463,10 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
     int fgrp = int(b0 / a.kb);
     int fkb = b0 - fgrp * a.kb;
     const uint8_t* fptr = a.native + ((long long)fkb * a.n16 + fgrp * kWarps + warp) * kBlockBytes;
-    int fault = (a.fault_step >= 0 && blockIdx.x == 0 && warp == 0) ? a.fault_step : -1;   // test hook, see StreamArgs
-    auto request = [&](int slot) {
+    const int fault = (a.fault_step >= 0 && blockIdx.x == 0 && warp == 0) ? a.fault_step : -1;   // test hook, see StreamArgs
+    auto request = [&](int slot, bool skip = false) {
         mbar_expect_tx(bar0 + slot * 8, kBlockBytes);
-        if (fault-- != 0) bulk_copy_g2s(ring0 + slot * kBlockBytes, fptr, kBlockBytes, bar0 + slot * 8);
+        if (!skip) bulk_copy_g2s(ring0 + slot * kBlockBytes, fptr, kBlockBytes, bar0 + slot * 8);
         ++fetch;
         fptr += stride;
         if (++fkb == a.kb) {
@@ -476,7 +481,7 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 #pragma unroll
         for (int s = 0; s < kStages; ++s)
-            if (fetch < wb1) request(s);
+            if (fetch < wb1) request(s, s == fault);       // (test hook: one of the first copies left out)
     }
     __syncwarp();
     if (a.overlap) {
@@ -668,16 +673,16 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
     }
 }
 
-template <int MT, bool XVEC, int W, bool H16 = false>
+template <int MT, bool XVEC, int W, bool H16 = false, bool XROWS = false>
 __global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
 w4a16_stream_kernel(const StreamArgs a) {
-    stream_body<MT, XVEC, W, H16, false>(a, nullptr);
+    stream_body<MT, XVEC, W, H16, false, XROWS>(a, nullptr);
 }
 
-template <int MT, int W, bool H16>
+template <int MT, int W, bool H16, bool XROWS = false>
 __global__ void __launch_bounds__(W * 32, (W == 16 ? B2_STREAM_CTAS16 : 4))
 w4a16_stream_gather_kernel(const StreamArgs a, const GatherArgs ga) {
-    stream_body<MT, true, W, H16, true>(a, &ga);
+    stream_body<MT, true, W, H16, true, XROWS>(a, &ga);
 }
 
 }  // namespace b2
