@@ -491,7 +491,10 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
         if (whole_x) stage_x<MT, XVEC, W, false>(xs, a, 0, a.kb * kBlockCols, xrows, kChunk);
     }
 
-    float acc[MT][4];
+    // With one row tile of x the sixteen MMAs of a block would be ONE dependent chain; two accumulator tiles used
+    // in turn make it two chains of eight (with more row tiles the tiles are independent chains already).
+    constexpr bool kTwoChains = MT == 1;
+    float acc[MT][4], acc2[kTwoChains ? MT : 1][4];
     int stage = 0;
     uint32_t parity = 0;
     bool failed = false;
@@ -511,7 +514,10 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
+            for (int c = 0; c < 4; ++c) {
+                acc[mt][c] = 0.0f;
+                if constexpr (kTwoChains) acc2[mt][c] = 0.0f;
+            }
 
         for (int p0 = k_lo; p0 < k_hi; p0 += kPhaseBlocks) {
             const int p1 = min(k_hi, p0 + kPhaseBlocks);
@@ -560,12 +566,19 @@ __device__ __forceinline__ void stream_body(const StreamArgs& a, const GatherArg
                                                dq_odd<H16>(and_or(ub, 0x00F000F0u, 0x64006400u), gh)};
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt)
-                            mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
+                            if (e == 0 || !kTwoChains) mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
+                            else mma_16816(acc2[mt], w, xv[mt].z, xv[mt].w, acc2[mt]);
                     }
                 }
             }
         }
 
+        if constexpr (kTwoChains) {            // (a fixed order: results do not depend on timing)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[mt][c] += acc2[mt][c];
+        }
         if (active && !failed) {
             const bool whole = (k_lo == 0 && k_hi == a.kb);
             bool write_out = whole;
