@@ -131,11 +131,18 @@ w4a16_tile_kernel(const TileArgs a) {
     // units = half blocks, dealt in consecutive runs to the warps
     const int units = kbn * 2;
     const int u0 = (units * warp) / a.warps, u1 = (units * (warp + 1)) / a.warps;
-    float acc[MT][4];
+    // The eight MMAs of a unit would be one dependent chain per row tile of x; kChains accumulator tiles used in
+    // turn cut it into chains of 8 / kChains (four at one row tile, two at two), added in a fixed order at the end.
+    constexpr int kChains = MT == 1 ? 4 : 2;
+    float acc[MT][4], accx[kChains - 1][MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
+        for (int c = 0; c < 4; ++c) {
+            acc[mt][c] = 0.0f;
+#pragma unroll
+            for (int q = 0; q < kChains - 1; ++q) accx[q][mt][c] = 0.0f;
+        }
     bool failed = false;
     for (int u = u0; u < u1 && !failed; ++u) {
         const int b = u >> 1, h = u & 1;
@@ -166,12 +173,21 @@ w4a16_tile_kernel(const TileArgs a) {
                                        dq_even<H16>(and_or(ub, 0x000F000Fu, 0x64006400u), gh),
                                        dq_odd<H16>(and_or(ua, 0x00F000F0u, 0x64006400u), gg),
                                        dq_odd<H16>(and_or(ub, 0x00F000F0u, 0x64006400u), gh)};
+                const int chain = (kChains == 4 ? 2 * (i & 1) + e : e);       // compile-time under the unrolling
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-                    mma_16816(acc[mt], w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, acc[mt]);
+                for (int mt = 0; mt < MT; ++mt) {
+                    float (&dst)[4] = chain == 0 ? acc[mt] : accx[chain == 0 ? 0 : chain - 1][mt];
+                    mma_16816(dst, w, e ? xv[mt].z : xv[mt].x, e ? xv[mt].w : xv[mt].y, dst);
+                }
             }
         }
     }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int q = 0; q < kChains - 1; ++q) acc[mt][c] += accx[q][mt][c];
     // Blocks this CTA requested but no warp waited for cannot exist: every block has two units.
     if (__syncthreads_or(failed) && threadIdx.x == 0) {
         // A warp gave up: copies of this CTA may still be in flight.  Look at every block's barrier
