@@ -359,9 +359,47 @@ int launch_tile_one(const b2::TileArgs& a, int smem, cudaStream_t s) {
     return B2_OK;
 }
 
+template <int MT, bool FULL, bool H16>
+int launch_tile_gather_one(const b2::TileArgs& a, const b2::GatherArgs& ga, int smem, cudaStream_t s) {
+    auto kernel = b2::w4a16_tile_gather_kernel<MT, FULL, H16>;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemLimit);
+        if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(a.n16) * unsigned(a.ksplit), 1, 1);
+    cfg.blockDim = dim3(unsigned(a.warps) * 32, 1, 1);
+    cfg.dynamicSmemBytes = size_t(smem);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int count = 0;
+    if (a.ksplit > 1) {
+        attr[count].id = cudaLaunchAttributeClusterDimension;
+        attr[count].val.clusterDim.x = unsigned(a.ksplit); attr[count].val.clusterDim.y = 1; attr[count].val.clusterDim.z = 1;
+        ++count;
+    }
+    if (a.overlap) {
+        attr[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = unsigned(count);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, a, ga);
+    if (le != cudaSuccess) return cuda_fail("w4a16_tile_gather_kernel", le);
+    return B2_OK;
+}
+
 int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ldy, int64_t rows,
              const b2::Dims& d, void* workspace, bool xvec, cudaStream_t s, const void* bias, int act = 0, int sms = 148,
-             bool h16 = false, bool overlap = false) {
+             bool h16 = false, bool overlap = false, const b2::GatherArgs* ga = nullptr) {
+    if (ga && (!xvec || act)) return kNotFused;       // the gather form exists for an aligned x and the plain output
     b2::TileArgs a;
     a.act = act;
     a.overlap = overlap ? 1 : 0;
@@ -382,6 +420,10 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     a.warps = kb_cta * 2 < b2::kTileMaxWarps ? kb_cta * 2 : b2::kTileMaxWarps;
     if (a.ksplit > 1) {
         const int smem2 = b2::tile_smem_bytes(kb_cta, mt * 8, a.warps) + a.ksplit * mt * 512;      // padded rows: the grid is small
+        if (ga) {
+            if (mt == 1) return h16 ? launch_tile_gather_one<1, true, true>(a, *ga, smem2, s) : launch_tile_gather_one<1, true, false>(a, *ga, smem2, s);
+            return h16 ? launch_tile_gather_one<2, true, true>(a, *ga, smem2, s) : launch_tile_gather_one<2, true, false>(a, *ga, smem2, s);
+        }
         if (h16 && xvec) return mt == 1 ? launch_tile_one<1, true, true, true>(a, smem2, s) : launch_tile_one<2, true, true, true>(a, smem2, s);
         if (mt == 1) return xvec ? launch_tile_one<1, true, true>(a, smem2, s) : launch_tile_one<1, false, true>(a, smem2, s);
         return xvec ? launch_tile_one<2, true, true>(a, smem2, s) : launch_tile_one<2, false, true>(a, smem2, s);
@@ -392,6 +434,14 @@ int run_tile(const void* x, int64_t ldx, const void* native, void* y, int64_t ld
     const int per_sm = padded <= kTileSmemLimit ? std::min(227 * 1024 / (padded + 1024), 2048 / (a.warps * 32)) : 0;
     const bool full = rows == mt * 8 || int64_t(d.n16) <= int64_t(per_sm) * (sms > 0 ? sms : 148);
     const int smem = b2::tile_smem_bytes(d.kb, full ? mt * 8 : int(rows), a.warps);
+    if (ga) {
+        if (mt == 1) {
+            if (full) return h16 ? launch_tile_gather_one<1, true, true>(a, *ga, smem, s) : launch_tile_gather_one<1, true, false>(a, *ga, smem, s);
+            return h16 ? launch_tile_gather_one<1, false, true>(a, *ga, smem, s) : launch_tile_gather_one<1, false, false>(a, *ga, smem, s);
+        }
+        if (full) return h16 ? launch_tile_gather_one<2, true, true>(a, *ga, smem, s) : launch_tile_gather_one<2, true, false>(a, *ga, smem, s);
+        return h16 ? launch_tile_gather_one<2, false, true>(a, *ga, smem, s) : launch_tile_gather_one<2, false, false>(a, *ga, smem, s);
+    }
     if (h16 && xvec) {
         if (mt == 1) return full ? launch_tile_one<1, true, true, true>(a, smem, s) : launch_tile_one<1, true, false, true>(a, smem, s);
         return full ? launch_tile_one<2, true, true, true>(a, smem, s) : launch_tile_one<2, true, false, true>(a, smem, s);
@@ -969,13 +1019,13 @@ int linear_impl(const void* x, int64_t ldx, const void* native, const void* bias
             return fail(B2_ERR_UNSUPPORTED, "no fused gate/up epilogue for this problem: run b2_w4a16_linear, then b2_w4a16_silu_mul_pairs");
         route = B2_ROUTE_STREAM;
     }
-    if (ga && route != B2_ROUTE_STREAM) return kNotFused;     // only the streaming kernel carries the gather
+    if (ga && route != B2_ROUTE_STREAM && route != B2_ROUTE_TILE) return kNotFused;     // the decode kernels carry the gather
     if (route == B2_ROUTE_TILE) {
         if (!tile_applicable(m, d, tile_split))
             return fail(B2_ERR_UNSUPPORTED, "the tile route needs M <= 16 and a layer whose K range fits in shared memory");
         const bool xvec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) && (d.k % 8 == 0);
         return run_tile(x, ldx, native, y, ldy, m, d, workspace, xvec, static_cast<cudaStream_t>(stream), bias, act, dev.sm_count, h16,
-                        (flags & B2_FLAG_OVERLAP_LAUNCH) != 0);
+                        (flags & B2_FLAG_OVERLAP_LAUNCH) != 0, ga);
     }
     if (route == B2_ROUTE_STREAM)
         return run_stream(x, ldx, native, y, ldy, m, d, workspace, workspace_bytes,
@@ -1194,7 +1244,7 @@ int b2_w4a16_linear_gather_launches(int64_t m, int64_t n_total, int64_t slice_co
     DeviceInfo dev;
     if (device_info(dev) != B2_OK) dev.sm_count = 148;
     const b2::Dims d = b2::make_dims(cols, k);
-    if (tile_applicable(m, d, tile_ksplit(d, dev.sm_count, pair_available()))) return 2;
+    if (tile_applicable(m, d, tile_ksplit(d, dev.sm_count, pair_available()))) return 1;
     const StreamPlan p = plan_stream(m, d, dev.sm_count);
     return (p.warps == 16 || p.warps == 4) && p.nchunks <= 1 ? 1 : 2;
 }

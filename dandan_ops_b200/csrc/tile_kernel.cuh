@@ -57,12 +57,63 @@ __host__ __device__ constexpr int tile_smem_bytes(int kb, int rows, int warps) {
            warps * (rows <= 8 ? 1 : 2) * 512;
 }
 
+// Element e of a row tile's 16 x (8 * MT) sums (fragment order: e = mt * 128 + 4 * lane + c) -> one output.
+// GATHER: threads e and e ^ 16 hold neighbouring columns of the same row; they exchange their values so that
+// the even one has a 4-byte word, which it stores into the local buffer and sends to every peer's mailbox.
+// Every lane of a warp must call this in the same iteration (the callers' loops guarantee it).
+template <bool GATHER>
+__device__ __forceinline__ void tile_emit(const TileArgs& a, const GatherArgs* ga, int nt, int e, float sum) {
+    const int mt = e >> 7, rl = (e >> 2) & 31, c = e & 3;
+    const int rg = rl >> 2, rt = rl & 3;
+    const int m = mt * 8 + 2 * rt + (c & 1), n = nt * 16 + rg + 8 * (c >> 1);
+    const bool inside = m < a.m && n < a.n;
+    if constexpr (!GATHER) {
+        if (inside) a.y[int64_t(m) * a.ldy + n] = finish_output(sum, a.bias, n);
+    } else {
+        const unsigned v = inside ? unsigned(__half_as_ushort(finish_output(sum, a.bias, n))) : 0u;
+        const unsigned other = __shfl_xor_sync(0xffffffffu, v, 16);          // column n ^ 1 of the same row
+        if ((rg & 1) == 0 && inside) {
+            const unsigned word = v | (other << 16);
+            *reinterpret_cast<unsigned*>(a.y + int64_t(m) * a.ldy + n) = word;
+            const unsigned epoch = mailbox_epoch(*ga);
+            const int64_t s = int64_t(m) * (ga->cols >> 1) + (n >> 1);
+            for (int q = 0; q < ga->world; ++q)
+                if (q != ga->rank)
+                    mailbox_send(mailbox(ga->flags[q], ga->world, ga->slots, epoch & 1u, ga->rank) + s, word, epoch);
+        }
+    }
+}
+
+// End of a writer CTA in the gather form: count it; the last one of the grid's n16 writers collects the peers'
+// packets with all its threads and publishes the epoch.
+__device__ __forceinline__ void tile_collect(const TileArgs& a, const GatherArgs* ga) {
+    __shared__ int last;
+    unsigned* mine = ga->flags[ga->rank];
+    const unsigned epoch = mailbox_epoch(*ga);                   // read before this CTA counts itself
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(mine + kGatherTicketWord, 1u) == unsigned(a.n16) - 1u;
+    __syncthreads();
+    if (!last) return;
+    if (mailbox_receive(*ga, epoch, threadIdx.x, blockDim.x)) atomicOr(mine + kGatherStatusWord, kStatusPeerTimeout);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mine[kGatherEpochWord] = epoch;
+        mine[kGatherTicketWord] = 0u;
+    }
+}
+
 // FULL: all MT * 8 rows of x are staged (zeros beyond M): compile-time layout, no row predicates -
 // the faster form whenever the padded rows do not cost occupancy.  Otherwise only the M rows that
 // exist are staged and lanes of missing rows use zero fragments.
-template <int MT, bool XVEC, bool FULL, bool H16 = false>
-__global__ void __launch_bounds__(kTileMaxWarps * 32)
-w4a16_tile_kernel(const TileArgs a) {
+//
+// GATHER: the multi-GPU form (b2_w4a16_linear_gather).  `a.y` is this rank's column slice of a full [M, N]
+// buffer; the CTA that writes a row tile stores it there and sends it to every peer's mailbox as
+// {word, epoch} packets (tile_emit).  The grid of this kernel need not be resident at once, so no CTA may wait
+// for a peer while others are still to be scheduled: the CTAs count themselves on the flag block's ticket
+// when their tile is out, and only the LAST one - by then every packet of this rank has left - collects the
+// packets the peers sent (bounded as everywhere) and publishes the epoch.
+template <int MT, bool XVEC, bool FULL, bool H16, bool GATHER>
+__device__ __forceinline__ void tile_body(const TileArgs& a, const GatherArgs* ga) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int rows = FULL ? MT * 8 : a.m;
     const int kChunk = tile_x_chunk_bytes(rows);
@@ -240,13 +291,11 @@ w4a16_tile_kernel(const TileArgs a) {
             return;
         }
         for (int e = threadIdx.x; e < MT * 128; e += blockDim.x) {
-            const int mt = e >> 7, rl = (e >> 2) & 31, c = e & 3;
             float sum = tot[e];
             for (int p = 0; p + 1 < a.ksplit; ++p) sum += peer[p * (MT * 128) + e];
-            const int rg = rl >> 2, rt = rl & 3;
-            const int m = mt * 8 + 2 * rt + (c & 1), n = nt * 16 + rg + 8 * (c >> 1);
-            if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(sum, a.bias, n);
+            tile_emit<GATHER>(a, ga, nt, e, sum);
         }
+        if constexpr (GATHER) tile_collect(a, ga);
         return;
     }
     // thread e adds element e of every warp's tile in warp order and stores one output
@@ -272,10 +321,21 @@ w4a16_tile_kernel(const TileArgs a) {
         float sum = 0.0f;
         for (int w = 0; w < a.warps; ++w)
             sum += reinterpret_cast<const float*>(red)[((w * MT + mt) * 32 + rl) * 4 + c];
-        const int rg = rl >> 2, rt = rl & 3;
-        const int m = mt * 8 + 2 * rt + (c & 1), n = nt * 16 + rg + 8 * (c >> 1);
-        if (m < a.m && n < a.n) a.y[int64_t(m) * a.ldy + n] = finish_output(sum, a.bias, n);
+        tile_emit<GATHER>(a, ga, nt, e, sum);
     }
+    if constexpr (GATHER) tile_collect(a, ga);
+}
+
+template <int MT, bool XVEC, bool FULL, bool H16 = false>
+__global__ void __launch_bounds__(kTileMaxWarps * 32)
+w4a16_tile_kernel(const TileArgs a) {
+    tile_body<MT, XVEC, FULL, H16, false>(a, nullptr);
+}
+
+template <int MT, bool FULL, bool H16>
+__global__ void __launch_bounds__(kTileMaxWarps * 32)
+w4a16_tile_gather_kernel(const TileArgs a, const GatherArgs ga) {
+    tile_body<MT, true, FULL, H16, true>(a, &ga);
 }
 
 }  // namespace b2

@@ -1,5 +1,5 @@
 """`b2_w4a16_linear_gather` on one GPU: the column-sharded projection and the all-gather as ONE launch
-(w4a16_stream_gather_kernel), with the peers played by the test.  All buffers and flag blocks are local
+(w4a16_stream_gather_kernel, w4a16_tile_gather_kernel), with the peers played by the test.  All buffers and flag blocks are local
 memory; the "peers'" packets are written into this rank's mailbox by the host before the launch, so the
 kernel never waits for another kernel.  Checked: the gathered `[M, N]` (own slice bit-equal to the plain
 projection and within the reference's tolerance of the CPU oracle, peers' slices as sent), the packets this
@@ -79,6 +79,13 @@ CASES = [  # world, rank, m, n_total, slice_cols, k, bias, fp16 steps
     (4, 2, 16, 1024, 256, 28680, True, False),       # 4-warp CTAs, two row tiles of x, ragged K
     (4, 3, 5, 4096, 1024, 28672, False, True),       # FP16-step chain
     (8, 5, 13, 2048, 256, 28672, False, False),
+    # layers of the tile kernel: one CTA per row tile, or a cluster of 2 or 4 that splits K
+    (2, 0, 1, 2048, 1024, 2048, False, False),
+    (2, 1, 8, 1990, 1008, 1024, True, False),
+    (4, 2, 16, 1024, 256, 2048, True, False),
+    (8, 5, 13, 2048, 256, 1032, False, False),
+    (4, 0, 3, 8192, 2048, 4096, True, True),
+    (2, 1, 6, 96, 48, 3072, True, False),
 ]
 
 
@@ -119,13 +126,13 @@ def test_one_launch_computes_sends_and_collects(world, rank, m, n_total, slice_c
     assert _native.gather_status(mine_flag.data_ptr()) == 0 and _native.status() == 0
 
 
-def test_layers_of_the_tile_kernel_take_two_launches_with_the_same_result():
+def test_unaligned_x_takes_two_launches_with_the_same_result():
     world, rank, m, n_total, slice_cols, k = 2, 0, 8, 2048, 1024, 2048
-    assert _native.linear_gather_launches(m, n_total, slice_cols, k, rank, world, MAILBOX) == 2
     peers = Peers(world, rank, m, n_total, slice_cols)
     layer = _layer(slice_cols, k, 5, True)
     g = torch.Generator().manual_seed(9)
-    x = torch.randn(m, k, generator=g).half().cuda()
+    x = torch.randn(m, k + 8, generator=g).half().cuda()[:, 1:k + 1]       # rows start 2 bytes off a 16-byte boundary
+    assert x.data_ptr() % 16 != 0 and x.stride(0) == k + 8
     theirs = peers.play_peers(1, g)
     before = _native.load().b2_w4a16_launch_count()
     _run(peers, layer, x, k)
