@@ -73,28 +73,31 @@ def _run(peers, layer, x, k):
                           peers.slice_cols, bias=layer._bias_fp16(), flags=layer._image_flags)
 
 
-CASES = [  # world, rank, m, n_total, slice_cols, k, bias, fp16 steps
-    (2, 0, 1, 2048, 1024, 28672, False, False),      # 16-warp CTAs
-    (2, 1, 8, 1990, 1008, 28672, True, False),       # short last slice, ragged last tile
-    (4, 2, 16, 1024, 256, 28680, True, False),       # 4-warp CTAs, two row tiles of x, ragged K
-    (4, 3, 5, 4096, 1024, 28672, False, True),       # FP16-step chain
-    (8, 5, 13, 2048, 256, 28672, False, False),
-    # layers of the tile kernel: one CTA per row tile, or a cluster of 2 or 4 that splits K
-    (2, 0, 1, 2048, 1024, 2048, False, False),
-    (2, 1, 8, 1990, 1008, 1024, True, False),
-    (4, 2, 16, 1024, 256, 2048, True, False),
-    (8, 5, 13, 2048, 256, 1032, False, False),
-    (4, 0, 3, 8192, 2048, 4096, True, True),
-    (2, 1, 6, 96, 48, 3072, True, False),
+CASES = [  # world, rank, m, n_total, slice_cols, k, bias, fp16 steps, launches
+    (2, 0, 1, 2048, 1024, 28672, False, False, 1),      # streaming kernel, 16-warp CTAs
+    (2, 1, 8, 1990, 1008, 28672, True, False, 1),       # short last slice, ragged last tile
+    (4, 2, 16, 1024, 256, 28680, True, False, 1),       # 4-warp CTAs, two row tiles of x, ragged K
+    (4, 3, 5, 4096, 1024, 28672, False, True, 1),       # FP16-step chain
+    (8, 5, 13, 2048, 256, 28672, False, False, 1),
+    # layers of the tile kernel (one CTA per row tile, or a cluster of 2 or 4 that splits K): one launch while the
+    # last CTA can collect the peers' packets in a single round, else projection + gather kernel
+    (2, 0, 1, 2048, 1024, 2048, False, False, 1),
+    (2, 1, 2, 1990, 1008, 1024, True, False, 1),
+    (4, 2, 1, 1024, 256, 2048, True, False, 1),
+    (8, 5, 1, 2048, 256, 1032, False, False, 1),
+    (4, 0, 1, 4096, 1024, 4096, True, True, 1),
+    (2, 1, 6, 96, 48, 3072, True, False, 1),
+    (4, 2, 16, 1024, 256, 2048, True, False, 2),
+    (2, 1, 8, 1990, 1008, 1024, True, False, 2),
 ]
 
 
-@pytest.mark.parametrize("world,rank,m,n_total,slice_cols,k,with_bias,h16", CASES)
-def test_one_launch_computes_sends_and_collects(world, rank, m, n_total, slice_cols, k, with_bias, h16):
+@pytest.mark.parametrize("world,rank,m,n_total,slice_cols,k,with_bias,h16,launches", CASES)
+def test_one_call_computes_sends_and_collects(world, rank, m, n_total, slice_cols, k, with_bias, h16, launches):
     peers = Peers(world, rank, m, n_total, slice_cols)
     lo, hi = peers.cols(rank)
     layer = _layer(hi - lo, k, 11 * world + rank + m, with_bias, h16)
-    assert _native.linear_gather_launches(m, n_total, slice_cols, k, rank, world, MAILBOX) == 1
+    assert _native.linear_gather_launches(m, n_total, slice_cols, k, rank, world, MAILBOX) == launches
     g = torch.Generator().manual_seed(1000 + m)
     mine_flag = peers.flags[rank]
     for epoch in range(1, 4):
@@ -103,7 +106,7 @@ def test_one_launch_computes_sends_and_collects(world, rank, m, n_total, slice_c
         theirs = peers.play_peers(epoch, g)
         before = _native.load().b2_w4a16_launch_count()
         _run(peers, layer, x, k)
-        assert _native.load().b2_w4a16_launch_count() - before == 1
+        assert _native.load().b2_w4a16_launch_count() - before == launches
         torch.cuda.synchronize()
         full = peers.bufs[rank]
         assert torch.equal(full[:, lo:hi], want_own)
