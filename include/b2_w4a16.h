@@ -284,10 +284,12 @@ int b2_w4a16_gather_wait_limit(int64_t microseconds);      /* <= 0 restores the 
  * rank, where this rank's `native` image holds its rows [rank * slice_cols, min(n_total, (rank + 1) *
  * slice_cols)) of W and `bias_fp16` (optional) those entries of the bias.  Arguments as b2_w4a16_gather and
  * b2_w4a16_linear_flags; `ld` is the row stride of the gathered buffers.
- * Decode sizes (m <= 16, a slice that fits a mailbox half, K % 8 == 0, an aligned x, a layer the streaming
- * kernel takes) run as one launch, w4a16_stream_gather_kernel: the warp that completes a 16-column tile stores it
+ * Decode sizes (m <= 16, a slice that fits a mailbox half, K % 8 == 0, an aligned x) run as one launch.
+ * Layers of the streaming kernel, w4a16_stream_gather_kernel: the warp that completes a 16-column tile stores it
  * into the local buffer and sends it to every peer's mailbox as {word, epoch} packets while the rest of the
  * weight stream is still running; CTAs that have finished their range poll the packets the peers sent.
+ * Layers of the tile kernel, w4a16_tile_gather_kernel: every CTA sends its tile, and the last CTA to finish
+ * collects the peers' packets - taken while that is a single round of four packets per thread.
  * The transfer overlaps the math tile by tile and the launch, fence and flag round trip of a separate gather
  * disappear.  Everything else runs the projection (b2_w4a16_linear_flags into the local slice) followed by
  * b2_w4a16_gather - same result, two launches; b2_w4a16_linear_gather_launches() says which (0 = bad arguments).
