@@ -265,3 +265,20 @@ def test_stream_plan_keeps_tickets_inside_the_ticket_area():
             if groups16 > plan["grid"]:                      # split row groups are indexed by CTA: grid * 16 tickets
                 assert plan["grid"] * 16 <= tickets, (n, k, m, plan)
             assert plan["k_splits"] >= 1 and plan["grid"] >= 1
+
+
+def test_gather_form_query_is_a_pure_function_of_the_problem():
+    """`b2_w4a16_linear_gather_launches`: which calls run projection and gather as one kernel.  Needs no GPU
+    (an unknown device counts as 148 SMs); every rank must get the same answer for equal slices."""
+    q = _native.linear_gather_launches
+    mailbox = 1 << 20
+    # decode sizes of the 70B MLP on 8 ranks: the streaming kernel carries the exchange
+    assert {q(m, 57344, 7168, 8192, r, 8, mailbox) for m in (1, 8, 16) for r in range(8)} == {1}
+    assert {q(m, 8192, 1024, 28672, r, 8, mailbox) for m in (1, 8) for r in range(8)} == {1}
+    # tile-kernel layers: one launch only while the last CTA collects in a single round of packets
+    assert q(1, 4096, 2048, 1024, 0, 2, mailbox) == 1 and q(8, 4096, 2048, 1024, 0, 2, mailbox) == 2
+    # more than 16 rows, or a slice that does not fit the mailbox: projection, then the gather kernel
+    assert q(17, 57344, 7168, 8192, 0, 8, mailbox) == 2 and q(8, 57344, 7168, 8192, 0, 8, 1024) == 2
+    # a rank without rows launches the gather alone; bad arguments give 0
+    assert q(4, 100, 16, 64, 7, 8, mailbox) == 1
+    assert q(0, 57344, 7168, 8192, 0, 8, mailbox) == 0 and q(8, 57344, 7168, 8192, 8, 8, mailbox) == 0
